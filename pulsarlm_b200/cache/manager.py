@@ -11,7 +11,10 @@ token in them is out of every future query's reach, and when the caller bounds
 the tokens a request brings to one step their pools are made only as large as
 `max_requests` such requests can fill (`window_pages`). Mixers that ask for a
 StateNeed get a row per request slot in a tensor [slots, *shape], zeroed when
-the slot is handed out.
+the slot is handed out. A layer whose parts keep several things (a mixer's cache
+beside the state of a filter in front of it) asks with a tuple of needs and gets
+a list of bindings in the same order; inside, such a holder is known by the key
+(layer, place in the tuple), a plain layer by its index.
 
 A request's life: `open` (a slot) -> `reserve(new_len)` before each step (pages
 for the step's tokens, all groups or none) -> `commit(new_len)` after it (length
@@ -73,6 +76,17 @@ class _Group:
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
 
 
+def flat_needs(needs: list) -> list[tuple]:
+    """(key, need) for every single need: key = layer, or (layer, place) inside a tuple."""
+    out = []
+    for layer, need in enumerate(needs):
+        if isinstance(need, (tuple, list)):
+            out += [((layer, place), one) for place, one in enumerate(need)]
+        else:
+            out.append((layer, need))
+    return out
+
+
 def window_pages(window: int, page_size: int, step_tokens: int, max_requests: int) -> int:
     """Pages that `max_requests` requests can hold at once in a group whose queries
     reach `window` keys back, when no request brings more than `step_tokens` tokens to
@@ -97,18 +111,19 @@ def cache_bytes(needs: list, n_pages: int, page_size: int, step_tokens: int | No
     (without the padding pages)."""
     width = torch.empty((), dtype=dtype).element_size()
     layers: dict[KVCacheNeed, int] = {}
-    for need in needs:
+    for _, need in flat_needs(needs):
         if isinstance(need, KVCacheNeed):
             layers[need] = layers.get(need, 0) + 1
     return sum(pool_pages(need, n_pages, page_size, step_tokens, max_requests)
-               * count * 2 * need.n_kv_heads * page_size * need.head_dim * width for need, count in layers.items())
+               * count * need.planes * need.n_kv_heads * page_size * need.head_dim * width
+               for need, count in layers.items())
 
 
 class CacheManager:
     def __init__(self, needs: list, page_size: int, n_pages: int, max_requests: int, dtype: torch.dtype,
                  device: torch.device | str | None, allocate: bool = True, mass_decay: float | None = None,
                  step_tokens: int | None = None):
-        """needs: per layer KVCacheNeed, StateNeed or None. n_pages: pages of the pool
+        """needs: per layer KVCacheNeed, StateNeed or None, or a tuple of those. n_pages: pages of the pool
         of a group that keeps every key. step_tokens: the most tokens one request
         brings to a step, if the caller keeps to such a bound (a scheduler's token
         budget); a group with a window then gets `window_pages(...)` pages when that
@@ -135,11 +150,12 @@ class CacheManager:
         self.device = torch.device(device) if device is not None else None
         self.n_layers = len(needs)
         self.groups: list[_Group] = []
-        self.layer_group: dict[int, int] = {}
-        self.state_layers: dict[int, StateNeed] = {}
-        self.states: dict[int, torch.Tensor] = {}
+        self.layer_group: dict = {}          # holder key -> group index
+        self.state_layers: dict = {}         # holder key -> StateNeed
+        self.states: dict = {}               # holder key -> tensor [slots + 1, *shape]
+        self._tuple_layers = {layer: len(need) for layer, need in enumerate(needs) if isinstance(need, (tuple, list))}
         by_need: dict[KVCacheNeed, _Group] = {}
-        for layer, need in enumerate(needs):
+        for layer, need in flat_needs(needs):
             if isinstance(need, KVCacheNeed):
                 group = by_need.get(need)
                 if group is None:
@@ -160,7 +176,7 @@ class CacheManager:
             for group in self.groups:
                 n = group.need
                 group.tensor = torch.zeros(
-                    (len(group.layers), group.n_pages + 1, 2, n.n_kv_heads, page_size, n.head_dim), dtype=dtype,
+                    (len(group.layers), group.n_pages + 1, n.planes, n.n_kv_heads, page_size, n.head_dim), dtype=dtype,
                     device=device)
             if mass_decay is not None:
                 for group in self.groups:
@@ -170,8 +186,8 @@ class CacheManager:
                     group.weight_sum = torch.zeros(shape[:2], dtype=torch.float32, device=device)
                     group.step_weight = torch.zeros(shape[:2], dtype=torch.float32, device=device)
             for layer, need in self.state_layers.items():
-                self.states[layer] = torch.zeros((max_requests + 1, *need.shape), dtype=_STATE_DTYPES[need.dtype],
-                                                 device=device)
+                state_dtype = dtype if need.dtype == "engine" else _STATE_DTYPES[need.dtype]
+                self.states[layer] = torch.zeros((max_requests + 1, *need.shape), dtype=state_dtype, device=device)
         self._lib = core.library()
         windows = (ctypes.c_int32 * max(1, len(self.groups)))(
             *[g.need.window if g.need.window is not None else -1 for g in self.groups])
@@ -227,20 +243,31 @@ class CacheManager:
 
     # ------------------------------------------------------------------ bindings
     def bindings(self) -> list:
-        """Per layer: KVBinding, StateBinding or None, for `Model.bind_caches`."""
+        """Per layer: KVBinding, StateBinding or None (a list of those for a layer that
+        asked with a tuple), for `Model.bind_caches`."""
         n_layers = self.n_layers
-        out: list = [None] * n_layers
+        out: list = [[None] * self._tuple_layers[layer] if layer in self._tuple_layers else None
+                     for layer in range(n_layers)]
+
+        def put(key, binding) -> None:
+            if isinstance(key, tuple):
+                out[key[0]][key[1]] = binding
+            else:
+                out[key] = binding
+
         for layer, g in self.layer_group.items():
             group = self.groups[g]
             where = group.layers.index(layer)
-            out[layer] = KVBinding(g, group.tensor[where, :, 0], group.tensor[where, :, 1], self.page_size,
-                                   group.step_mass[where] if group.step_mass is not None else None,
-                                   group.step_weight[where] if group.step_weight is not None else None,
-                                   group.mass_sum[where] if group.mass_sum is not None else None,
-                                   group.weight_sum[where] if group.weight_sum is not None else None,
-                                   self.mass_decay)
+            # (a group of one plane keeps one row per token that is read as key and as value)
+            put(layer, KVBinding(g, group.tensor[where, :, 0], group.tensor[where, :, group.need.planes - 1],
+                                 self.page_size,
+                                 group.step_mass[where] if group.step_mass is not None else None,
+                                 group.step_weight[where] if group.step_weight is not None else None,
+                                 group.mass_sum[where] if group.mass_sum is not None else None,
+                                 group.weight_sum[where] if group.weight_sum is not None else None,
+                                 self.mass_decay))
         for layer in self.state_layers:
-            out[layer] = StateBinding(self.states[layer])
+            put(layer, StateBinding(self.states[layer]))
         return out
 
     def bytes_per_page(self) -> int:
@@ -250,7 +277,7 @@ class CacheManager:
     def group_bytes_per_page(self, group: int) -> int:
         g = self.groups[group]
         width = torch.empty((), dtype=self.dtype).element_size()
-        return len(g.layers) * 2 * g.need.n_kv_heads * self.page_size * g.need.head_dim * width
+        return len(g.layers) * g.need.planes * g.need.n_kv_heads * self.page_size * g.need.head_dim * width
 
     # ------------------------------------------------------------------ requests
     def open(self, request) -> int | None:

@@ -37,7 +37,7 @@ def register_architecture(
     model_types: tuple[str, ...] = (),
     replace: bool = False,
 ) -> Architecture:
-    """Makes `name` (config.json's `architectures[0]`) loadable; `model_types`
+    """Makes `name` (config.json's `architectures[0]`, or its `architecture`) loadable; `model_types`
     are `model_type` values that select it when `architectures` is absent."""
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture {name!r} is already registered")
@@ -52,7 +52,7 @@ def registered_architectures() -> list[str]:
 
 def find_architecture(text: dict) -> Architecture:
     """The architecture config.json names, or a ConfigError that lists what is known."""
-    names = text.get("architectures") or []
+    names = text.get("architectures") or text.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     for name in names:

@@ -73,7 +73,8 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
                                       scalar_t* __restrict__ out, int64_t out_row_stride, int n_heads, int group,
                                       int head_dim, int window, float scale, float softcap,
                                       float* __restrict__ mass_sum, float* __restrict__ weight_sum,
-                                      const float* __restrict__ query_weights, int32_t* status) {
+                                      const float* __restrict__ query_weights, const float* __restrict__ sinks,
+                                      const scalar_t* __restrict__ gate, int64_t gate_row_stride, int32_t* status) {
     extern __shared__ float q_shared[];  // [warps][head_dim]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -184,7 +185,24 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
         if (mass_sum != nullptr) {
             add_mass(mass_page, mass_max);
         }
-        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        if (sinks != nullptr) {
+            // A sink: one more term exp(sink) in the denominator, with no key and no value.
+            const float sink = sinks[h];
+            const float m_new = fmaxf(m, sink);
+            const float corr = m > -INFINITY ? expf(m - m_new) : 0.0f;
+            l = l * corr + expf(sink - m_new);
+#pragma unroll
+            for (int i = 0; i < kMaxAcc; ++i) {
+                if (i < n_acc) {
+                    acc[i] *= corr;
+                }
+            }
+        }
+        float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        if (gate != nullptr) {
+            // The head's output times sigmoid of its gate logit.
+            inv *= 1.0f / (1.0f + expf(-pl_load(gate + t * gate_row_stride + h)));
+        }
         scalar_t* orow = out + t * out_row_stride + static_cast<int64_t>(h) * head_dim;
 #pragma unroll
         for (int i = 0; i < kMaxAcc; ++i) {
@@ -206,13 +224,17 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
 // page a query attends, query_weights[t] (1 when nullptr) times the query's largest
 // scaled score in the page, per head, and the weight itself once per page
 // (pulsarlm-core/inc/pulsarlm/kernels/ops.hpp:150-160). softcap > 0: every scaled
-// score s becomes softcap * tanh(s / softcap) before the softmax (0: off).
+// score s becomes softcap * tanh(s / softcap) before the softmax (0: off). sinks (fp32
+// [n_heads], may be nullptr): exp(sinks[h]) is added to head h's softmax denominator. gate
+// ([T, n_heads] logits with gate_row_stride elements between rows, may be nullptr): head
+// h's output for token t is multiplied by sigmoid(gate[t, h]).
 PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
                              int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                              const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
                              void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
                              int head_dim, int window, float scale, float softcap, int dtype, float* mass_sum,
-                             float* weight_sum, const float* query_weights, int32_t* status, cudaStream_t stream) {
+                             float* weight_sum, const float* query_weights, const float* sinks, const void* gate,
+                             int64_t gate_row_stride, int32_t* status, cudaStream_t stream) {
     PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0 && page_size > 0,
                "attention: bad sizes tokens=%d heads=%d kv_heads=%d head_dim=%d page=%d", n_tokens, n_heads,
                n_kv_heads, head_dim, page_size);
@@ -234,7 +256,8 @@ PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_
             static_cast<const scalar_t*>(q), q_row_stride, static_cast<const scalar_t*>(k_pool),
             static_cast<const scalar_t*>(v_pool), page_stride, head_stride, page_size, n_pages, table, table_width,
             pos, entry, static_cast<scalar_t*>(out), out_row_stride, n_heads, group, head_dim, window, scale,
-            softcap, mass_sum, weight_sum, query_weights, status);
+            softcap, mass_sum, weight_sum, query_weights, sinks, static_cast<const scalar_t*>(gate), gate_row_stride,
+            status);
     });
     PL_CHECK_LAUNCH("attention");
     return 0;

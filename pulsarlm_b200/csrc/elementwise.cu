@@ -9,12 +9,12 @@
 
 namespace {
 
-// x[t, :] = table[tokens[t], :] as fp32. An id outside [0, vocab) writes zeros and
+// x[t, :] = table[tokens[t], :] * scale as fp32. An id outside [0, vocab) writes zeros and
 // raises bit 0 of *status (the host validates ids first; this only keeps a bad id
 // from reading outside the table).
 template <typename scalar_t>
 __global__ void embed_kernel(const scalar_t* __restrict__ table, const int32_t* __restrict__ tokens,
-                             float* __restrict__ x, int hidden, int vocab, int32_t* status) {
+                             float* __restrict__ x, int hidden, int vocab, float scale, int32_t* status) {
     pl_grid_trigger();
     pl_grid_wait();
     const int t = blockIdx.x;
@@ -31,7 +31,7 @@ __global__ void embed_kernel(const scalar_t* __restrict__ table, const int32_t* 
     }
     const scalar_t* src = table + static_cast<int64_t>(token) * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        row[i] = pl_load(src + i);
+        row[i] = pl_load(src + i) * scale;  // (scale 1 leaves the value as it is)
     }
 }
 
@@ -235,7 +235,7 @@ int norm_threads(int hidden) {
 }  // namespace
 
 PL_API int pl_embed(const void* table, const int32_t* tokens, float* x, int n_tokens, int hidden, int vocab,
-                    int dtype, int32_t* status, cudaStream_t stream) {
+                    float scale, int dtype, int32_t* status, cudaStream_t stream) {
     PL_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0, "embed: bad sizes tokens=%d hidden=%d vocab=%d", n_tokens,
                hidden, vocab);
     if (n_tokens == 0) {
@@ -244,7 +244,7 @@ PL_API int pl_embed(const void* table, const int32_t* tokens, float* x, int n_to
     const int threads = hidden >= 1024 ? 256 : 128;
     PL_DISPATCH_DTYPE(dtype, "embed", {
         pl_launch_overlapped(embed_kernel<scalar_t>, n_tokens, threads, 0, stream,
-                             static_cast<const scalar_t*>(table), tokens, x, hidden, vocab, status);
+                             static_cast<const scalar_t*>(table), tokens, x, hidden, vocab, scale, status);
     });
     PL_CHECK_LAUNCH("embed");
     return 0;
@@ -387,5 +387,55 @@ PL_API int pl_fill_random(void* out, int64_t n, int dtype, uint64_t seed, uint64
         fill_random_kernel<scalar_t><<<blocks, 256, 0, stream>>>(static_cast<scalar_t*>(out), n, key, scale, offset);
     });
     PL_CHECK_LAUNCH("fill_random");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Bias and activation of a plain projection: out = act(in + bias), fp32 inside.
+// act 0: none, 1: relu(z)^2, 2: tanh(z). Rows of `in` may be columns of a wider
+// matrix (in_row_stride elements apart); out is dense and may be `in` itself.
+namespace {
+
+template <typename scalar_t>
+__global__ void bias_act_kernel(const scalar_t* in, int64_t in_row_stride, const scalar_t* __restrict__ bias,
+                                scalar_t* out, int64_t tokens, int width, int act) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    const int64_t total = tokens * width;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t t = i / width;
+        const int c = static_cast<int>(i - t * width);
+        float z = pl_load(in + t * in_row_stride + c);
+        if (bias != nullptr) {
+            z += pl_load(bias + c);
+        }
+        if (act == 1) {
+            z = z > 0.0f ? z * z : 0.0f;
+        } else if (act == 2) {
+            z = tanhf(z);
+        }
+        pl_store(out + i, z);
+    }
+}
+
+}  // namespace
+
+PL_API int pl_bias_act(const void* in, int64_t in_row_stride, const void* bias, void* out, int n_tokens, int width,
+                       int act, int dtype, cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && width > 0 && act >= 0 && act <= 2 && in_row_stride >= width,
+               "bias_act: bad arguments tokens=%d width=%d act=%d", n_tokens, width, act);
+    if (n_tokens == 0) {
+        return 0;
+    }
+    const int threads = 256;
+    const int64_t total = static_cast<int64_t>(n_tokens) * width;
+    const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
+    PL_DISPATCH_DTYPE(dtype, "bias_act", {
+        pl_launch_overlapped(bias_act_kernel<scalar_t>, blocks, threads, 0, stream, static_cast<const scalar_t*>(in),
+                             in_row_stride, static_cast<const scalar_t*>(bias), static_cast<scalar_t*>(out),
+                             static_cast<int64_t>(n_tokens), width, act);
+    });
+    PL_CHECK_LAUNCH("bias_act");
     return 0;
 }

@@ -1,0 +1,133 @@
+// A short causal convolution over time on every channel, added to its own input:
+//
+//   out[t, c] = h[t, c] + sum_{j < taps} w[c, j] * h_seq[t - (taps - 1) + j, c]
+//
+// where h_seq is the sequence's input so far, zeros before its start. A step brings a
+// sequence's next rows (an entry's rows are consecutive and in order); the taps - 1 inputs
+// before them come from the sequence's state slot [taps - 1, width] (oldest first), which
+// a second kernel brings up to date afterwards. Products and sums are fp32, one rounding
+// on store. A row's result depends on the sequence's inputs alone, not on how they were
+// cut into steps or on the rest of the batch.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxTaps = 16;
+
+template <typename scalar_t>
+__global__ void short_conv_kernel(const scalar_t* __restrict__ h, const float* __restrict__ weight,
+                                  const scalar_t* __restrict__ state, const int32_t* __restrict__ entry,
+                                  const int32_t* __restrict__ slots, scalar_t* __restrict__ out, int n_tokens,
+                                  int width, int taps) {
+    const int t = blockIdx.x;
+    const int e = entry[t];
+    const int reach = taps - 1;
+    // How many of the rows before this one belong to the same sequence (up to `reach`).
+    int inside = 0;
+    while (inside < reach && t - inside - 1 >= 0 && entry[t - inside - 1] == e) {
+        ++inside;
+    }
+    const scalar_t* old = state + static_cast<int64_t>(slots[e]) * reach * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float* w = weight + static_cast<int64_t>(c) * taps;
+        const float own = pl_load(h + static_cast<int64_t>(t) * width + c);
+        float acc = 0.0f;
+        for (int j = 0; j < taps; ++j) {
+            const int back = reach - j;  // this tap reads the input `back` rows before
+            float v;
+            if (back == 0) {
+                v = own;
+            } else if (back <= inside) {
+                v = pl_load(h + static_cast<int64_t>(t - back) * width + c);
+            } else {
+                v = pl_load(old + static_cast<int64_t>(reach - (back - inside)) * width + c);
+            }
+            acc = fmaf(w[j], v, acc);
+        }
+        pl_store(out + static_cast<int64_t>(t) * width + c, own + acc);
+    }
+}
+
+// The state after the step: the last taps - 1 inputs of each sequence. A portion of at least
+// taps - 1 rows writes them from its last rows; a shorter one is handled by its first row's
+// block, which also moves the older rows up.
+template <typename scalar_t>
+__global__ void short_conv_state_kernel(const scalar_t* __restrict__ h, const int32_t* __restrict__ entry,
+                                        const int32_t* __restrict__ slots, scalar_t* __restrict__ state,
+                                        int n_tokens, int width, int taps) {
+    const int t = blockIdx.x;
+    const int e = entry[t];
+    const int reach = taps - 1;
+    int before = 0, after = 0;
+    while (before < reach && t - before - 1 >= 0 && entry[t - before - 1] == e) {
+        ++before;
+    }
+    while (after < reach && t + after + 1 < n_tokens && entry[t + after + 1] == e) {
+        ++after;
+    }
+    scalar_t* mine = state + static_cast<int64_t>(slots[e]) * reach * width;
+    // (both counts stop at `reach`: a count that got there means "at least")
+    if (before == reach || after == reach || before + 1 + after >= reach) {
+        // A portion of at least `reach` rows: each of its last `reach` rows writes itself.
+        if (after < reach) {
+            for (int c = threadIdx.x; c < width; c += blockDim.x) {
+                mine[static_cast<int64_t>(reach - 1 - after) * width + c] = h[static_cast<int64_t>(t) * width + c];
+            }
+        }
+        return;
+    }
+    if (before != 0) {
+        return;
+    }
+    // A portion of n < reach rows, and this is its first: rows move up by n, the new ones follow.
+    const int n = 1 + after;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        for (int j = 0; j < reach - n; ++j) {
+            mine[static_cast<int64_t>(j) * width + c] = mine[static_cast<int64_t>(j + n) * width + c];
+        }
+        for (int m = 0; m < n; ++m) {
+            mine[static_cast<int64_t>(reach - n + m) * width + c] = h[static_cast<int64_t>(t + m) * width + c];
+        }
+    }
+}
+
+}  // namespace
+
+// h, out [T, width] and state [slots, taps - 1, width] in the engine's dtype; weight fp32
+// [width, taps]; entry int32 [T] names each row's batch entry, slots int32 [entries] each
+// entry's state slot. out may not alias h. The state is read, not written.
+PL_API int pl_short_conv(const void* h, const float* weight, const void* state, const int32_t* entry,
+                         const int32_t* slots, void* out, int n_tokens, int width, int taps, int dtype,
+                         cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && width > 0 && taps >= 1 && taps <= kMaxTaps, "short_conv: bad sizes tokens=%d width=%d "
+               "taps=%d (at most %d)", n_tokens, width, taps, kMaxTaps);
+    if (n_tokens == 0) {
+        return 0;
+    }
+    const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
+    PL_DISPATCH_DTYPE(dtype, "short_conv", {
+        short_conv_kernel<scalar_t><<<n_tokens, threads, 0, stream>>>(
+            static_cast<const scalar_t*>(h), weight, static_cast<const scalar_t*>(state), entry, slots,
+            static_cast<scalar_t*>(out), n_tokens, width, taps);
+    });
+    PL_CHECK_LAUNCH("short_conv");
+    return 0;
+}
+
+// Brings every entry's state slot up to date with the step's inputs h (run after
+// pl_short_conv has read the old state).
+PL_API int pl_short_conv_state(const void* h, const int32_t* entry, const int32_t* slots, void* state, int n_tokens,
+                               int width, int taps, int dtype, cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && width > 0 && taps >= 1 && taps <= kMaxTaps, "short_conv_state: bad sizes tokens=%d "
+               "width=%d taps=%d", n_tokens, width, taps);
+    if (n_tokens == 0 || taps == 1) {
+        return 0;
+    }
+    const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
+    PL_DISPATCH_DTYPE(dtype, "short_conv_state", {
+        short_conv_state_kernel<scalar_t><<<n_tokens, threads, 0, stream>>>(
+            static_cast<const scalar_t*>(h), entry, slots, static_cast<scalar_t*>(state), n_tokens, width, taps);
+    });
+    PL_CHECK_LAUNCH("short_conv_state");
+    return 0;
+}

@@ -96,7 +96,7 @@ class ModelRunner:
         # `captures_state_steps()`; the capture's warm-up run then works on a copy of the states
         # and rows that pad a step use a slot no request holds. With attention mass measured,
         # steps are captured only if every mixer can measure inside one.
-        state_mixers = [self.model.blocks[layer].mixer for layer in cache.state_layers]
+        state_mixers = [self.model.cache_holder(key) for key in cache.state_layers]
         self.graphs_allowed = all(getattr(m, "captures_state_steps", lambda: False)() for m in state_mixers) and (
             cache.mass_decay is None or all(
                 getattr(part, "measures_mass_in_captured_steps", lambda: True)() for part in model.parts()))

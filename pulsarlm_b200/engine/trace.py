@@ -26,7 +26,7 @@ import sys
 
 
 DEFAULT_PAGE_SIZE = 16
-MAX_LIVE_REQUESTS = 16
+MAX_LIVE_REQUESTS = 4
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -40,6 +40,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     p.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE, help="tokens per cache page")
+    p.add_argument("--max-requests", type=int, default=MAX_LIVE_REQUESTS,
+                   help="most requests live at any time (state slots of the cache)")
     p.add_argument("--device", default="cuda:0")
     return p
 
@@ -77,7 +79,7 @@ def run(argv=None, stdin=None, stdout=None) -> int:
     else:
         model = load_model(args.model, dtype, device)
     n_pages = -(-args.max_tokens // args.page_size)
-    cache = CacheManager(model.cache_needs(), args.page_size, n_pages, MAX_LIVE_REQUESTS, dtype, device)
+    cache = CacheManager(model.cache_needs(), args.page_size, n_pages, args.max_requests, dtype, device)
     runner = ModelRunner(model, cache)
 
     for line in stdin:

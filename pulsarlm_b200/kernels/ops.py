@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 21
+ABI_VERSION = 22
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -35,7 +35,15 @@ class KernelError(RuntimeError):
 
 
 _SIGNATURES = {
-    "pl_embed": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR, _PTR],
+    "pl_embed": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR],
+    "pl_add_normed_rmsnorm": [_PTR, _PTR, _PTR, _PTR, _F32, _F32, _PTR, _F32, _PTR, _PTR, _I32, _I32, _I32, _PTR],
+    "pl_bias_act": [_PTR, _I64, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
+    "pl_short_conv": [_PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
+    "pl_short_conv_state": [_PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
+    "pl_delta_rule": [_PTR, _PTR, _PTR, _PTR, _PTR, _I64, _PTR, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR,
+                      _I64, _I32, _I32, _I32, _F32, _F32, _F32, _I32, _PTR],
+    "pl_norm_write_paged": [_PTR, _I64, _PTR, _F32, _PTR, _PTR, _PTR, _I32, _PTR, _I64, _I32, _I32, _I32, _I32, _I32,
+                            _PTR, _PTR],
     "pl_take_tokens": [_PTR, _PTR, _PTR, _I32, _I32, _PTR, _PTR],
     "pl_add_rmsnorm": [_PTR, _PTR, _PTR, _I32, _PTR, _PTR, _I32, _I32, _F32, _I32, _PTR],
     "pl_swiglu": [_PTR, _PTR, _I32, _I32, _I32, _PTR],
@@ -44,7 +52,8 @@ _SIGNATURES = {
     "pl_rope_kv_write": [_PTR, _PTR, _PTR, _I64, _PTR, _PTR, _PTR, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32,
                          _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR, _PTR, _F32, _PTR, _PTR],
     "pl_attention_simt": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
-                          _I32, _I32, _I32, _I32, _I32, _F32, _F32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR],
+                          _I32, _I32, _I32, _I32, _I32, _F32, _F32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _I64, _PTR,
+                          _PTR],
     "pl_attention_decode": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                             _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode_mass": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
@@ -186,13 +195,14 @@ def _dev(*tensors: torch.Tensor | None) -> None:
 
 # ----------------------------------------------------------------------------- ops
 
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, status: torch.Tensor | None = None) -> None:
-    """out[t] (fp32 [T, H]) = table[tokens[t]]; tokens int32 [T]."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, status: torch.Tensor | None = None,
+          scale: float = 1.0) -> None:
+    """out[t] (fp32 [T, H]) = table[tokens[t]] * scale; tokens int32 [T]."""
     _dev(table, tokens, out, status)
     assert table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32
     assert tokens.dtype == torch.int32 and tokens.is_contiguous()
     vocab, hidden = table.shape
-    _call("pl_embed", _p(table), _p(tokens), _p(out), tokens.numel(), hidden, vocab, _code(table.dtype),
+    _call("pl_embed", _p(table), _p(tokens), _p(out), tokens.numel(), hidden, vocab, float(scale), _code(table.dtype),
           _p(status), _stream())
 
 
@@ -222,6 +232,106 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
         assert rows.dtype == torch.int32 and rows.is_contiguous()
     _call("pl_add_rmsnorm", _p(x), _p(delta), _p(weight), _code(weight.dtype), _p(out), _p(rows), n_rows, hidden,
           float(eps), _code(out.dtype), _stream())
+
+
+def add_normed_rmsnorm(x: torch.Tensor, y: torch.Tensor, y_weight: torch.Tensor, mult: float, y_eps: float,
+                       weight: torch.Tensor | None, eps: float, out: torch.Tensor | None,
+                       rows: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> None:
+    """x fp32 [T, H] += mult * rmsnorm(y + bias) * y_weight (in place unless rows is given); out =
+    rmsnorm(x) * weight when out is given. y, bias and out in the engine's dtype, the weights fp32.
+    With rows (int32 [R]), output row r is made from source row rows[r] and x is left as it was."""
+    _dev(x, y, y_weight, weight, out, rows, bias)
+    hidden = x.shape[-1]
+    assert x.dtype == torch.float32 and x.is_contiguous() and y.shape == x.shape and y.is_contiguous()
+    assert y_weight.dtype == torch.float32 and y_weight.shape == (hidden,) and y_weight.is_contiguous()
+    n_rows = rows.numel() if rows is not None else x.shape[0]
+    if out is not None:
+        assert weight is not None and weight.dtype == torch.float32 and weight.shape == (hidden,)
+        assert weight.is_contiguous() and out.shape == (n_rows, hidden) and out.is_contiguous() and out.dtype == y.dtype
+    if bias is not None:
+        assert bias.dtype == y.dtype and bias.shape == (hidden,) and bias.is_contiguous()
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.is_contiguous()
+    _call("pl_add_normed_rmsnorm", _p(x), _p(y), _p(bias), _p(y_weight), float(mult), float(y_eps), _p(weight),
+          float(eps), _p(out), _p(rows), n_rows, hidden, _code(y.dtype), _stream())
+
+
+BIAS_ACT = {"none": 0, "relu2": 1, "tanh": 2}
+
+
+def bias_act(x: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, act: str = "none") -> None:
+    """out = act(x + bias) over [T, N]; act "none", "relu2" (the square of relu) or "tanh". x may be
+    columns of a wider matrix (row stride free); out is dense and may be x."""
+    _dev(x, bias, out)
+    tokens, width = x.shape
+    assert out.shape == x.shape and out.dtype == x.dtype and x.stride(1) == 1 and out.is_contiguous()
+    if bias is not None:
+        assert bias.shape == (width,) and bias.dtype == x.dtype and bias.is_contiguous()
+    _call("pl_bias_act", _p(x), x.stride(0) if tokens > 1 else width, _p(bias), _p(out), tokens, width, BIAS_ACT[act],
+          _code(x.dtype), _stream())
+
+
+def short_conv(h: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, entry: torch.Tensor, slots: torch.Tensor,
+               out: torch.Tensor) -> None:
+    """out = h + causal convolution of h over time per channel; h, out [T, W], weight fp32 [W, taps],
+    state [slots, taps - 1, W] the inputs before this step's rows (read only)."""
+    _dev(h, weight, state, entry, slots, out)
+    tokens, width = h.shape
+    taps = weight.shape[1]
+    assert weight.dtype == torch.float32 and weight.shape == (width, taps) and weight.is_contiguous()
+    assert h.is_contiguous() and out.is_contiguous() and out.shape == h.shape and out.dtype == h.dtype == state.dtype
+    assert state.is_contiguous() and state.shape[1:] == (taps - 1, width) and out.data_ptr() != h.data_ptr()
+    assert entry.dtype == torch.int32 and slots.dtype == torch.int32 and entry.numel() == tokens
+    _call("pl_short_conv", _p(h), _p(weight), _p(state), _p(entry), _p(slots), _p(out), tokens, width, taps,
+          _code(h.dtype), _stream())
+
+
+def short_conv_state(h: torch.Tensor, entry: torch.Tensor, slots: torch.Tensor, state: torch.Tensor) -> None:
+    """state[slot] <- the last taps - 1 inputs of each entry's sequence after this step's rows h."""
+    _dev(h, entry, slots, state)
+    tokens, width = h.shape
+    taps = state.shape[1] + 1
+    assert h.is_contiguous() and state.is_contiguous() and state.dtype == h.dtype and state.shape[2] == width
+    _call("pl_short_conv_state", _p(h), _p(entry), _p(slots), _p(state), tokens, width, taps, _code(h.dtype),
+          _stream())
+
+
+def delta_rule(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, a_pre: torch.Tensor,
+               w_pre: torch.Tensor, w0: torch.Tensor, a0: torch.Tensor, norm: torch.Tensor, state: torch.Tensor,
+               first_rows: torch.Tensor, counts: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, n_heads: int,
+               dim: int, decay_scale: float, unit_eps: float, eps: float) -> None:
+    """The generalized delta rule over each entry's rows in order (see csrc/delta_rule.cu). r, k, v,
+    g, a_pre [T, heads * dim] share one row stride; state fp32 [slots, heads, dim, dim] is updated."""
+    _dev(r, k, v, g, a_pre, w_pre, w0, a0, norm, state, first_rows, counts, slots, out)
+    width = n_heads * dim
+    stride = r.stride(0)
+    for t in (r, k, v, g, a_pre):
+        assert t.shape[1] == width and t.stride(1) == 1 and t.stride(0) == stride and t.dtype == out.dtype
+    assert w_pre.shape[1] == width and w_pre.stride(1) == 1 and w_pre.dtype == out.dtype
+    for t in (w0, a0, norm):
+        assert t.dtype == torch.float32 and t.shape == (width,) and t.is_contiguous()
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (n_heads, dim, dim)
+    assert out.shape[1] == width and out.stride(1) == 1
+    n_entries = first_rows.numel()
+    assert counts.numel() == n_entries and slots.numel() >= n_entries
+    _call("pl_delta_rule", _p(r), _p(k), _p(v), _p(g), _p(a_pre), stride, _p(w_pre), w_pre.stride(0), _p(w0), _p(a0),
+          _p(norm), _p(state), _p(first_rows), _p(counts), _p(slots), _p(out), out.stride(0), n_entries, n_heads, dim,
+          float(decay_scale), float(unit_eps), float(eps), _code(out.dtype), _stream())
+
+
+def norm_write_paged(z: torch.Tensor, weight: torch.Tensor, eps: float, pos: torch.Tensor, entry: torch.Tensor,
+                     table: torch.Tensor, pool: torch.Tensor, page_size: int,
+                     status: torch.Tensor | None = None) -> None:
+    """pool[page of (entry, pos)] <- rmsnorm(z) * weight; z [T, rank] (row stride free), weight fp32
+    [rank], pool [pages, 1, page_size, rank]."""
+    _dev(z, weight, pos, entry, table, pool, status)
+    tokens, rank = z.shape
+    assert z.stride(1) == 1 and weight.dtype == torch.float32 and weight.shape == (rank,) and weight.is_contiguous()
+    assert pool.dtype == z.dtype and pool.shape[1:] == (1, page_size, rank) and pool.stride(3) == 1
+    assert pool.stride(2) == rank and table.dim() == 2 and table.is_contiguous()
+    _call("pl_norm_write_paged", _p(z), z.stride(0), _p(weight), float(eps), _p(pos), _p(entry), _p(table),
+          table.shape[1], _p(pool), pool.stride(0), page_size, pool.shape[0], rank, tokens, _code(z.dtype),
+          _p(status), _stream())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -363,13 +473,19 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
                    pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
                    scale: float, status: torch.Tensor | None = None, mass_sum: torch.Tensor | None = None,
                    weight_sum: torch.Tensor | None = None, query_weights: torch.Tensor | None = None,
-                   softcap: float = 0.0) -> None:
+                   softcap: float = 0.0, sinks: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> None:
     """Causal paged attention; q and out [T, nh, hd] (row strides free), pools
     [pages, nkv, page_size, hd]. With mass_sum fp32 [pages, nh] and weight_sum fp32
     [pages], the attention mass of every attended page is added to them
     (query_weights fp32 [T], all 1 when None). softcap > 0: scaled scores pass through
-    softcap * tanh(s / softcap) before the softmax."""
-    _dev(q, k_pool, v_pool, table, pos, entry, out, status, mass_sum, weight_sum, query_weights)
+    softcap * tanh(s / softcap) before the softmax. sinks fp32 [nh]: exp(sinks[h]) joins head
+    h's softmax denominator (a term with no key and no value). gate [T, nh] logits (row
+    stride free): head h's output for token t is multiplied by sigmoid(gate[t, h])."""
+    _dev(q, k_pool, v_pool, table, pos, entry, out, status, mass_sum, weight_sum, query_weights, sinks, gate)
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.shape == (q.shape[1],) and sinks.is_contiguous()
+    if gate is not None:
+        assert gate.dtype == q.dtype and gate.shape == (q.shape[0], q.shape[1]) and gate.stride(1) == 1
     if mass_sum is not None:
         assert mass_sum.dtype == torch.float32 and mass_sum.shape == (k_pool.shape[0], q.shape[1])
         assert mass_sum.is_contiguous() and weight_sum is not None and weight_sum.dtype == torch.float32
@@ -388,7 +504,8 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
     _call("pl_attention_simt", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
           page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
           n_heads, n_kv, head_dim, int(window or 0), float(scale), float(softcap or 0.0), _code(q.dtype),
-          _p(mass_sum), _p(weight_sum), _p(query_weights), _p(status), _stream())
+          _p(mass_sum), _p(weight_sum), _p(query_weights), _p(sinks), _p(gate),
+          gate.stride(0) if gate is not None else 0, _p(status), _stream())
 
 
 def attention_decode_supports(head_dim: int, group: int, page_size: int, dtype: torch.dtype) -> bool:

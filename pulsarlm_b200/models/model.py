@@ -139,8 +139,20 @@ class Model:
 
     # ------------------------------------------------------------------ cache
     def cache_needs(self) -> list:
-        """Per layer: the mixer's KVCacheNeed, StateNeed or None."""
-        return [b.mixer.cache_need() for b in self.blocks]
+        """Per layer: the mixer's KVCacheNeed, StateNeed or None; for a block whose other
+        parts keep state too (`cache_holders()`), a tuple with every holder's need."""
+        out = []
+        for b in self.blocks:
+            holders = getattr(b, "cache_holders", None)
+            out.append(tuple(h.cache_need() for h in holders()) if holders is not None else b.mixer.cache_need())
+        return out
+
+    def cache_holder(self, key):
+        """The part behind a cache manager's holder key: a layer's mixer, or for the key
+        (layer, place) that place among the block's cache holders."""
+        if isinstance(key, tuple):
+            return self.blocks[key[0]].cache_holders()[key[1]]
+        return self.blocks[key].mixer
 
     def cache_sources(self) -> list[int | None]:
         """Per layer: the layer whose cache it reads instead of its own, or None."""
@@ -149,13 +161,16 @@ class Model:
         for layer, src in enumerate(sources):
             if src is None:
                 continue
-            if not 0 <= src < len(self.blocks) or needs[src] is None or sources[src] is not None:
+            if not 0 <= src < len(self.blocks) or needs[src] is None or sources[src] is not None or (
+                    isinstance(needs[src], tuple) and needs[src][0] is None):
                 raise ValueError(f"layer {layer} reads the cache of layer {src}, which keeps none of its own")
             # The reader must see the cache as its owner keeps it: the same heads and head
             # size, and no further back than the owner's window (pages behind that window
             # are given back while the request runs).
             reads = getattr(self.blocks[layer].mixer, "cache_read_need", None)
             want, have = (reads() if reads is not None else None), needs[src]
+            if isinstance(have, tuple):
+                have = have[0]  # (a block's cache holders start with its mixer)
             if want is not None and hasattr(have, "n_kv_heads"):
                 if (want.n_kv_heads, want.head_dim) != (have.n_kv_heads, have.head_dim):
                     raise ValueError(
@@ -181,8 +196,17 @@ class Model:
         sources = self.cache_sources()
         for layer, b in enumerate(self.blocks):
             src = sources[layer] if sources[layer] is not None else layer
-            if bindings[src] is not None:
-                b.mixer.bind_cache(bindings[src])
+            if hasattr(b, "cache_holders"):
+                mine = list(bindings[layer])
+                if src != layer:
+                    theirs = bindings[src]
+                    mine[0] = theirs[0] if isinstance(theirs, list) else theirs
+                for holder, binding in zip(b.cache_holders(), mine):
+                    if binding is not None:
+                        holder.bind_cache(binding)
+            elif bindings[src] is not None:
+                theirs = bindings[src]
+                b.mixer.bind_cache(theirs[0] if isinstance(theirs, list) else theirs)
 
     # ------------------------------------------------------------------ forward
     def forward(self, batch: StepBatch) -> torch.Tensor | None:

@@ -6,6 +6,7 @@ names the spec gives; none knows the model around it.
 
 from __future__ import annotations
 
+import dataclasses
 import math
 
 import torch
@@ -16,10 +17,25 @@ from .registry import BuildContext, Part, register_part
 from .spec import PartSpec, TensorNeed
 
 
+@dataclasses.dataclass
+class NormedDelta:
+    """A sublayer's output that enters the residual stream normed and scaled:
+    x += mult * rmsnorm(y + bias) * weight (weight fp32, eps the norm's). A block hands
+    it on in the place of a plain delta; the next norm's kernel does the norm, the add
+    and its own norm in one pass."""
+
+    y: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+    mult: float = 1.0
+    bias: torch.Tensor | None = None
+
+
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
     """h = v * rsqrt(mean(v^2) + eps) * weight over the fp32 residual stream, with
-    the pending layer output added first (v = x + delta, x updated in place).
+    the pending layer output added first (v = x + delta, x updated in place; a
+    NormedDelta is normed and scaled on its way in).
     params: hidden_size, eps. tensors: weight [hidden_size].
     Formula: pulsarlm-core/src/kernels/rmsnorm.cu:29-49."""
 
@@ -35,13 +51,27 @@ class RMSNorm(Part):
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         self.weight = tensors[self.spec.tensors["weight"]].contiguous()
+        self._weight_f32: torch.Tensor | None = None
 
-    def forward(self, x: torch.Tensor, delta: torch.Tensor | None = None,
+    def weight_f32(self) -> torch.Tensor:
+        if self._weight_f32 is None:
+            self._weight_f32 = self.weight.float().contiguous()
+        return self._weight_f32
+
+    def forward(self, x: torch.Tensor, delta: "torch.Tensor | NormedDelta | None" = None,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
         n = rows.numel() if rows is not None else x.shape[0]
         out = torch.empty((n, self.hidden), dtype=self.ctx.dtype, device=x.device)
-        ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
+        if isinstance(delta, NormedDelta):
+            ops.add_normed_rmsnorm(x, delta.y, delta.weight, delta.mult, delta.eps, self.weight_f32(), self.eps, out,
+                                   rows, delta.bias)
+        else:
+            ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
         return out
+
+    def pending(self, y: torch.Tensor, mult: float = 1.0, bias: torch.Tensor | None = None) -> NormedDelta:
+        """`y` as a residual contribution normed by this norm: mult * rmsnorm(y + bias) * weight."""
+        return NormedDelta(y, self.weight_f32(), self.eps, mult, bias)
 
 
 def rope_inverse_frequencies(theta: float, head_dim: int, rotary_dim: int, llama3: dict | None) -> list[float]:
@@ -99,13 +129,15 @@ class NoPosition(Part):
 
 @register_part("embedding", "table")
 class Embedding(Part):
-    """x[t] = weight[token[t]], unscaled (pulsarlm-core/src/engine/model/llama.cpp:86),
-    written as fp32 into the residual stream. params: vocab_size, hidden_size."""
+    """x[t] = weight[token[t]] * scale (pulsarlm-core/src/engine/model/llama.cpp:86 has
+    no scale), written as fp32 into the residual stream. params: vocab_size,
+    hidden_size, scale (optional, 1 when absent)."""
 
     def __init__(self, spec: PartSpec, ctx: BuildContext):
         super().__init__(spec, ctx)
         self.vocab = int(self.param("vocab_size"))
         self.hidden = int(self.param("hidden_size"))
+        self.scale = float(spec.params.get("scale") or 1.0)
         self.weight: torch.Tensor | None = None
 
     @classmethod
@@ -119,7 +151,7 @@ class Embedding(Part):
         """`batch`: the step (an embedding that adds learned positions or scales by a
         constant of the configuration reads batch.pos); this one uses its status word."""
         x = torch.empty((tokens.numel(), self.hidden), dtype=torch.float32, device=tokens.device)
-        ops.embed(self.weight, tokens, x, batch.status if batch is not None else None)
+        ops.embed(self.weight, tokens, x, batch.status if batch is not None else None, self.scale)
         return x
 
 
@@ -195,3 +227,52 @@ class GatedMLP(Part):
 
     def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
         return gated_feed_forward(h, self.gate_up, self.down)
+
+
+@register_part("feed_forward", "mlp")
+class PlainMLP(Part):
+    """act(h Wu^T + bu) Wd^T + bd: an ungated feed-forward. params: hidden_size,
+    intermediate_size, activation ("relu2": the square of relu), bias (whether both
+    projections have one). tensors: up [I, H], down [H, I], up_bias [I], down_bias [H].
+    The down projection's bias is added by `output_bias()`'s taker when the block
+    takes it (a norm kernel that follows), else here."""
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.hidden = int(self.param("hidden_size"))
+        self.inter = int(self.param("intermediate_size"))
+        self.activation = str(spec.params.get("activation", "relu2"))
+        if self.activation not in ("relu2",):
+            raise ValueError(f"mlp: unsupported activation {self.activation!r} (supported: 'relu2')")
+        self.has_bias = bool(spec.params.get("bias", False))
+        self.up: torch.Tensor | None = None
+        self.down: torch.Tensor | None = None
+        self.up_bias: torch.Tensor | None = None
+        self.down_bias: torch.Tensor | None = None
+
+    @classmethod
+    def tensor_needs(cls, spec: PartSpec) -> dict[str, TensorNeed]:
+        h, i = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        t = spec.tensors
+        needs = {t["up"]: TensorNeed((i, h)), t["down"]: TensorNeed((h, i))}
+        if spec.params.get("bias"):
+            needs[t["up_bias"]] = TensorNeed((i,), role="offset")
+            needs[t["down_bias"]] = TensorNeed((h,), role="offset")
+        return needs
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        t = self.spec.tensors
+        self.up = tensors[t["up"]].contiguous()
+        self.down = tensors[t["down"]].contiguous()
+        if self.has_bias:
+            self.up_bias = tensors[t["up_bias"]].to(self.ctx.dtype).contiguous()
+            self.down_bias = tensors[t["down_bias"]].to(self.ctx.dtype).contiguous()
+
+    def forward(self, h: torch.Tensor, batch, bias_taken: bool = False) -> torch.Tensor:
+        """bias_taken: the caller adds `down_bias` itself (inside the kernel that reads the output)."""
+        z = linear(h, self.up)
+        ops.bias_act(z, self.up_bias, z, self.activation)
+        y = linear(z, self.down)
+        if self.down_bias is not None and not bias_taken:
+            ops.bias_act(y, self.down_bias, y, "none")
+        return y

@@ -50,3 +50,75 @@ class PreNormBlock:
         mixed = self.mixer.forward(h, batch)
         h = self.ff_norm.forward(x, mixed)
         return x, self.feed_forward.forward(h, batch)
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock:
+    """Every sublayer is normed before and after, and its normed output enters the
+    residual stream scaled:
+
+        x += m * norm_mixer_out(mixer(filter_mixer(norm_mixer(x))))
+        x += m * norm_ff_out(feed_forward(filter_ff(norm_ff(x))))
+
+    Norm names in the LayerSpec: "mixer", "mixer_out", "feed_forward", "feed_forward_out".
+    `extras` of the LayerSpec: "residual_mult" (m, 1 when absent) and optional PartSpecs
+    "mixer_filter" / "feed_forward_filter" of the "filter" registry (e.g. a short
+    convolution over time), applied to the sublayer's input. A LayerSpec whose
+    feed_forward is None has the first line only. The out-norm of a sublayer is not run
+    on its own: its output travels as a NormedDelta and the next norm kernel norms it,
+    adds it and norms the sum for the next sublayer in one pass."""
+
+    def __init__(self, spec: LayerSpec, ctx: BuildContext):
+        self.spec = spec
+        extras = spec.extras or {}
+        self.mult = float(extras.get("residual_mult", 1.0))
+        self.mixer_norm = build_part("norm", spec.norms["mixer"], ctx)
+        self.mixer_out_norm = build_part("norm", spec.norms["mixer_out"], ctx)
+        self.mixer = build_part("mixer", spec.mixer, ctx)
+        self.mixer_filter = build_part("filter", extras["mixer_filter"], ctx) if extras.get("mixer_filter") else None
+        self.feed_forward = self.ff_norm = self.ff_out_norm = self.ff_filter = None
+        if spec.feed_forward is not None:
+            self.ff_norm = build_part("norm", spec.norms["feed_forward"], ctx)
+            self.ff_out_norm = build_part("norm", spec.norms["feed_forward_out"], ctx)
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, ctx)
+            if extras.get("feed_forward_filter"):
+                self.ff_filter = build_part("filter", extras["feed_forward_filter"], ctx)
+
+    @classmethod
+    def part_specs(cls, spec: LayerSpec):
+        extras = spec.extras or {}
+        out = [("norm", spec.norms["mixer"]), ("norm", spec.norms["mixer_out"]), ("mixer", spec.mixer)]
+        if extras.get("mixer_filter"):
+            out.append(("filter", extras["mixer_filter"]))
+        if spec.feed_forward is not None:
+            out += [("norm", spec.norms["feed_forward"]), ("norm", spec.norms["feed_forward_out"]),
+                    ("feed_forward", spec.feed_forward)]
+            if extras.get("feed_forward_filter"):
+                out.append(("filter", extras["feed_forward_filter"]))
+        return out
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer_out_norm, self.mixer, self.mixer_filter, self.ff_norm,
+                            self.ff_out_norm, self.feed_forward, self.ff_filter) if p is not None]
+
+    def cache_holders(self):
+        """The parts that keep something per request, the mixer first."""
+        return [self.mixer] + [f for f in (self.mixer_filter, self.ff_filter) if f is not None]
+
+    def forward(self, x: torch.Tensor, delta, batch):
+        h = self.mixer_norm.forward(x, delta)
+        if self.mixer_filter is not None:
+            h = self.mixer_filter.forward(h, batch)
+        delta = self.mixer_out_norm.pending(self.mixer.forward(h, batch), self.mult)
+        if self.feed_forward is None:
+            return x, delta
+        h = self.ff_norm.forward(x, delta)
+        if self.ff_filter is not None:
+            h = self.ff_filter.forward(h, batch)
+        # A bias on the feed-forward's last projection is added by the kernel that norms its output.
+        bias = getattr(self.feed_forward, "down_bias", None)
+        if bias is not None:
+            y = self.feed_forward.forward(h, batch, bias_taken=True)
+        else:
+            y = self.feed_forward.forward(h, batch)
+        return x, self.ff_out_norm.pending(y, self.mult, bias)

@@ -22,6 +22,9 @@ Interfaces (duck-typed; the base classes below document them):
 * mixer:       `cache_need() -> KVCacheNeed | StateNeed | None`,
                `bind_cache(binding)`, `forward(h, batch) -> [T, H]` engine dtype.
 * feed_forward:`forward(h, batch) -> [T, H]` engine dtype.
+* filter:      something a block puts in front of a sublayer's input (a short convolution
+               over time): `forward(h, batch) -> [T, H]` engine dtype, and like a mixer
+               `cache_need()` / `bind_cache(binding)` when it keeps state per request.
 * block:       `forward(x, delta, batch) -> (x, delta)`: the arrangement of
                norms, mixer and feed-forward around the residual stream.
 """
@@ -35,7 +38,7 @@ import torch
 
 from .spec import PartSpec, TensorNeed
 
-_KINDS = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+_KINDS = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "filter")
 _REGISTRIES: dict[str, dict[str, type]] = {k: {} for k in _KINDS}
 
 
@@ -69,7 +72,7 @@ def _load_builtins() -> None:
     global _builtins_loaded
     if not _builtins_loaded:
         _builtins_loaded = True
-        from . import attention, basic, block  # noqa: F401
+        from . import attention, basic, block, delta_rule, latent_attention, short_conv  # noqa: F401
 
 
 def part_class(kind: str, name: str) -> type:

@@ -26,12 +26,15 @@ class PartSpec:
 @dataclasses.dataclass
 class LayerSpec:
     """One layer: an arrangement (`block`, e.g. "pre_norm") of a mixer, a
-    feed-forward and the norms the arrangement names."""
+    feed-forward (None where the arrangement allows a layer without one) and the norms
+    the arrangement names. `extras`: whatever else the arrangement takes (constants,
+    PartSpecs of further parts), by the names it documents."""
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None
     norms: dict[str, PartSpec]
+    extras: dict[str, Any] = dataclasses.field(default_factory=dict)
 
 
 @dataclasses.dataclass
@@ -57,8 +60,9 @@ class TensorNeed:
     """What a part expects of one checkpoint tensor. `role` is "matrix" for
     operands of matrix products and embedding tables (converted to the engine's
     dtype) or "vector" for scales and the like (a tensor stored in 32-bit stays
-    32-bit) or "ignored" for a tensor that may be stored but is not read.
-    `optional` tensors may be missing."""
+    32-bit), "offset" for biases and other vectors around zero (kept like "vector";
+    random weights draw them around 0 instead of 1), or "ignored" for a tensor that may
+    be stored but is not read. `optional` tensors may be missing."""
 
     shape: tuple[int, ...]
     role: str = "matrix"
@@ -71,18 +75,22 @@ class KVCacheNeed:
     and as many values. `window` = None keeps every token; a number keeps only the
     last `window` tokens readable, and pages wholly before them are given back.
     `n_heads` is the number of query heads that read the cache; the cache manager
-    sizes the optional per-page attention-mass accumulators by it."""
+    sizes the optional per-page attention-mass accumulators by it. `planes` = 2 keeps
+    keys and values; 1 keeps one row per token that serves as both (a mixer that caches
+    a shared latent)."""
 
     n_kv_heads: int
     head_dim: int
     window: int | None = None
     n_heads: int = 0
+    planes: int = 2
 
 
 @dataclasses.dataclass(frozen=True)
 class StateNeed:
-    """A mixer that keeps a state of fixed size per request: `shape` elements of
-    `dtype` ("float32" or "bfloat16"), zeroed when a request gets its slot."""
+    """A part that keeps a state of fixed size per request: `shape` elements of
+    `dtype` ("float32", "bfloat16", "int32", or "engine" for the engine's dtype), zeroed
+    when a request gets its slot."""
 
     shape: tuple[int, ...]
     dtype: str = "float32"

@@ -45,9 +45,16 @@ def stored_dtype_for(need: TensorNeed, stored: torch.dtype, engine_dtype: torch.
         return torch.int32
     if engine_dtype == torch.float32:
         return torch.float32
-    if need.role == "vector" and stored in (torch.float32, torch.float64):
+    if need.role in ("vector", "offset") and stored in (torch.float32, torch.float64):
         return torch.float32
     return engine_dtype
+
+
+def shape_fits(stored, wanted) -> bool:
+    """Whether a stored shape is the wanted one; a wanted extent of -1 takes any (a size that
+    only the checkpoint gives: the part reads it off the tensor when it loads)."""
+    stored, wanted = tuple(stored), tuple(wanted)
+    return len(stored) == len(wanted) and all(w == -1 or s == w for s, w in zip(stored, wanted))
 
 
 def check_names(where: str, needs: dict[str, TensorNeed], shapes: dict[str, tuple[int, ...]]) -> None:
@@ -55,7 +62,7 @@ def check_names(where: str, needs: dict[str, TensorNeed], shapes: dict[str, tupl
     missing = [n for n, need in needs.items() if n not in shapes and not need.optional]
     unexpected = [n for n in shapes if n not in needs]
     wrong = [(n, shapes[n], need.shape) for n, need in needs.items()
-             if n in shapes and tuple(shapes[n]) != tuple(need.shape)]
+             if n in shapes and not shape_fits(shapes[n], need.shape)]
     if missing or unexpected or wrong:
         raise WeightsError(where, missing, unexpected, wrong)
 

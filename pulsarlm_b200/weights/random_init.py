@@ -68,6 +68,8 @@ def random_tensors(
         t = torch.empty(need.shape, dtype=dtype, device=device)
         if need.role == "vector":
             fill_random(t, seed, name, vector_std, 1.0)
+        elif need.role == "offset":
+            fill_random(t, seed, name, vector_std)
         else:
             fill_random(t, seed, name, std)
         yield name, t
