@@ -529,8 +529,204 @@ def run_ours(args) -> dict:
     }
 
 
+# ----------------------------------------------------------------------------- --design rerilorn
+def rerilorn_config(width: int, layers: int, vocab: int = 32000) -> dict:
+    """A Rerilorn model at a real model's layer sizes: every third layer a delta-rule layer
+    (heads of 64), the others latent attention (16 heads of 64 over a latent of 128, window
+    1,024), feed-forward 4 x width, four taps."""
+    delta = {"type": "general_delta", "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 64},
+             "mlp": {"kind": "dense", "ff": 4 * width}}
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": 16, "dim": 64, "vdim": 64, "kv_rank": 128, "mask": {"size": 1024}, "scale": 0.125},
+              "mlp": {"kind": "dense", "ff": 4 * width}}
+    return {"architecture": "Rerilorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "embedding": {"scale": float(width) ** 0.5}, "canon": {"taps": 4},
+            "layers": [delta if i % 3 == 0 else latent for i in range(layers)]}
+
+
+def llama_config_like(width: int, layers: int, vocab: int = 32000) -> dict:
+    """The Llama decoder at the same width, depth and vocabulary: heads of 64 in groups of
+    four, gated feed-forward of 8/3 x width (the parameters of a plain one of 4 x width)."""
+    cfg = dict(LLAMA32_1B)
+    cfg.update({"num_hidden_layers": layers, "hidden_size": width, "num_attention_heads": width // 64,
+                "num_key_value_heads": max(1, width // 256), "head_dim": 64,
+                "intermediate_size": (8 * width // 3 + 255) // 256 * 256, "vocab_size": vocab,
+                "tie_word_embeddings": True, "rope_scaling": None, "max_position_embeddings": 8192})
+    return cfg
+
+
+def time_kernel(fn, reps: int = 20, warmup: int = 3) -> float:
+    """Milliseconds per call, CUDA events around `reps` calls after `warmup`; a 256 MB buffer is
+    rewritten between calls so that no call finds its inputs in L2."""
+    import torch
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")
+    for _ in range(warmup):
+        fn()
+    total = 0.0
+    for _ in range(reps):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        total += start.elapsed_time(end)
+    return total / reps
+
+
+def design_kernels(width: int, pk: dict) -> dict:
+    """The new design's kernels alone at one layer's sizes, beside the like kernel of the
+    Llama layer where there is one: milliseconds, algorithmic bytes, fraction of the copy
+    bandwidth."""
+    import torch
+
+    from pulsarlm_b200.kernels import ops
+
+    dev, bf = "cuda:0", torch.bfloat16
+    out: dict = {}
+
+    def note(name, ms, nbytes):
+        out[name] = {"ms": ms, "bytes": nbytes, "frac_of_hbm": nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"]}
+
+    for tokens, entries in ((2048, 1), (64, 64)):
+        tag = f"T{tokens}_E{entries}"
+        per = tokens // entries
+        entry = torch.arange(entries, dtype=torch.int32, device=dev).repeat_interleave(per)
+        slots = torch.arange(entries, dtype=torch.int32, device=dev)
+        first = torch.arange(0, tokens, per, dtype=torch.int32, device=dev)
+        count = torch.full((entries,), per, dtype=torch.int32, device=dev)
+        x = torch.randn((tokens, width), device=dev)
+        y = torch.randn((tokens, width), device=dev).to(bf)
+        h = torch.empty_like(y)
+        w32 = torch.ones(width, device=dev)
+        note(f"add_normed_rmsnorm_{tag}", time_kernel(lambda: ops.add_normed_rmsnorm(x, y, w32, 0.5, 1e-6, w32, 1e-6, h)),
+             tokens * width * (4 + 4 + 2 + 2))
+        note(f"add_rmsnorm_{tag} (Llama)", time_kernel(lambda: ops.add_rmsnorm(x, y, w32, 1e-6, h)),
+             tokens * width * (4 + 4 + 2 + 2))
+        state = torch.zeros((entries + 1, 3, width), dtype=bf, device=dev)
+        cw = torch.randn((width, 4), device=dev)
+
+        def conv():
+            ops.short_conv(y, cw, state, entry, slots, h)
+            ops.short_conv_state(y, entry, slots, state)
+        note(f"short_conv_{tag}", time_kernel(conv), tokens * width * 4 + entries * 3 * width * 4)
+        heads = width // 64
+        proj = torch.randn((tokens, 5 * width + 64), device=dev).to(bf)
+        w_pre = torch.randn((tokens, width), device=dev).to(bf)
+        S = torch.zeros((entries + 1, heads, 64, 64), device=dev)
+        o = torch.empty((tokens, width), dtype=bf, device=dev)
+        parts = [proj[:, i * width:(i + 1) * width] for i in range(5)]
+        note(f"delta_rule_{tag}",
+             time_kernel(lambda: ops.delta_rule(*parts, w_pre, w32, w32, w32, S, first, count, slots, o, heads, 64,
+                                                0.6065, 1e-6, 1e-6)),
+             tokens * width * 2 * 7 + entries * heads * 64 * 64 * 4 * 2)
+    # attention of 64 single tokens over 1,024 keys: 16 heads over a latent of 128 with sink,
+    # gate and split weights, beside 16 heads in 4 groups over keys and values of 128 without
+    page, keys, batch = 16, 1024, 64
+    n_pages = batch * keys // page
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, keys // page)
+    pos = torch.full((batch,), keys - 1, dtype=torch.int32, device=dev)
+    ent = torch.arange(batch, dtype=torch.int32, device=dev)
+    q = torch.randn((batch, 16, 128), device=dev).to(bf)
+    res = torch.empty_like(q)
+    latent = torch.randn((n_pages, 1, page, 128), device=dev).to(bf)
+    sinks = torch.zeros(16, device=dev)
+    gate = torch.zeros((batch, 16), dtype=bf, device=dev)
+    extras = ops.attention_extras(q, sinks, gate, True)
+    for splits in (1, 2, 4):
+        scratch = torch.empty(ops.attention_decode_scratch_floats(batch, 16, 128, splits), device=dev)
+        note(f"attention_decode_latent_b64_k1024_splits{splits}",
+             time_kernel(lambda: ops.attention_decode(q, latent, latent, table, pos, ent, res, page, 1024, 0.1, splits,
+                                                      scratch, extras=extras)), batch * keys * 128 * 2)
+    kv = torch.randn((2, n_pages, 4, page, 128), device=dev).to(bf)
+    for splits in (1, 2, 4):
+        scratch = torch.empty(ops.attention_decode_scratch_floats(batch, 16, 128, splits), device=dev)
+        note(f"attention_decode_b64_k1024_splits{splits} (Llama, 4 kv heads)",
+             time_kernel(lambda: ops.attention_decode(q, kv[0], kv[1], table, pos, ent, res, page, 1024, 0.1, splits,
+                                                      scratch)), batch * keys * 4 * 128 * 2 * 2)
+    # a 2,048-token prompt: the tiled kernel over the latent with and without the extras
+    tokens = 2048
+    n_pages = tokens // page
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, n_pages)
+    q = torch.randn((tokens, 16, 128), device=dev).to(bf)
+    res = torch.empty_like(q)
+    latent = torch.randn((n_pages, 1, page, 128), device=dev).to(bf)
+    gate = torch.zeros((tokens, 16), dtype=bf, device=dev)
+    rows = ops.attention_prefill_tile_rows()
+    tiles = torch.tensor([(r, min(rows, tokens - r), r, 0) for r in range(0, tokens, rows)], dtype=torch.int32,
+                         device=dev)
+    flops = 4.0 * 16 * 128 * sum(min(p + 1, 1024) for p in range(tokens))
+    for name, ex in (("latent, sink, gate, split weights", ops.attention_extras(q, sinks, gate, True)),
+                     ("latent, sink, gate", ops.attention_extras(q, sinks, gate, False)), ("plain", None)):
+        ms = time_kernel(lambda: ops.attention_prefill(q, latent, latent, table, tiles, res, page, 1024, 0.1, extras=ex))
+        out[f"attention_prefill_T2048_w1024 ({name})"] = {"ms": ms, "tflops": flops / (ms / 1e3) / 1e12}
+    return out
+
+
+def run_design(args) -> dict:
+    """Prefill and decode throughput of the Rerilorn design at a few sizes beside the Llama
+    decoder at the same width, depth and vocabulary (random weights), and the design's own
+    kernels alone."""
+    import gc
+
+    import torch
+
+    from pulsarlm_b200 import Engine
+    from pulsarlm_b200.engine.runner import StepEntry
+
+    pk = peaks()
+    results: dict = {}
+    prompt, batch, context = 2048, 8, 2048
+    with ClockSampler() as clocks:
+        for width, layers in ((1024, 6), (2048, 6), (4096, 3)):
+            for name, cfg in (("rerilorn", rerilorn_config(width, layers)), ("llama", llama_config_like(width, layers))):
+                vocab = cfg.get("vocab", cfg.get("vocab_size"))
+                n_pages = (batch * (context + 256) + 4 * prompt) // PAGE_SIZE
+                engine = Engine(cfg, dtype="bfloat16", device="cuda:0", n_pages=n_pages, page_size=PAGE_SIZE,
+                                prefill_tokens_per_step=prompt, max_requests=batch + 2, seed=0)
+                gen = torch.Generator().manual_seed(1)
+                times = []
+                for attempt in range(args.warmup + 3):
+                    tokens = torch.randint(0, vocab, (prompt,), generator=gen).tolist()
+                    torch.cuda.synchronize()
+                    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record()
+                    engine.runner.step([StepEntry(("p", attempt), tokens, [prompt - 1])])
+                    end.record()
+                    torch.cuda.synchronize()
+                    engine.runner.end(("p", attempt))
+                    if attempt >= args.warmup:
+                        times.append(start.elapsed_time(end))
+                prefill_ms = statistics.median(times)
+                ids = fill_cache(engine, batch, context, name)
+                decode_ms, launches = time_decode(engine, ids, args.steps, args.warmup, vocab)
+                params = sum(int(t.numel()) for part in engine.model.parts() for t in vars(part).values()
+                             if isinstance(t, torch.Tensor))
+                results[f"{name}_w{width}_l{layers}"] = {
+                    "parameters": params, "prefill_ms": prefill_ms, "prefill_tok_s": prompt / (prefill_ms / 1e3),
+                    "decode_ms": decode_ms, "decode_tok_s": batch / (decode_ms / 1e3),
+                    "decode_launches_per_step": launches // max(1, args.steps),
+                    "graphs": bool(engine.cuda_graphs)}
+                del engine
+                gc.collect()
+                torch.cuda.empty_cache()
+        kernels = design_kernels(2048, pk)
+    summary = clocks.summary()
+    return {"metric": "prefill and decode tok/s of the Rerilorn design beside the Llama decoder at equal sizes",
+            "design": "rerilorn", "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "dtype": "bf16", "data": "synthetic: random weights drawn on the device, uniform random token ids",
+            "config": {"prompt": prompt, "decode_batch": batch, "decode_context": context, "page_size": PAGE_SIZE,
+                       "peaks": pk["source"], "l2": "kernels alone: a 256 MB buffer is rewritten between calls"},
+            "models": results, "kernels": kernels,
+            "clocks": {"sm_mhz": summary["sm_mhz"], "sm_max_mhz": summary["sm_max_mhz"], "reasons": summary["reasons"]}}
+
+
 def main() -> int:
     p = argparse.ArgumentParser()
+    p.add_argument("--design", default="llama", choices=["llama", "rerilorn"],
+                   help="llama: the headline workload (the default); rerilorn: that design's prefill and decode "
+                        "throughput at a few sizes beside the Llama decoder at equal sizes, and its kernels alone")
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=128)
     p.add_argument("--warmup", type=int, default=8)
@@ -552,6 +748,10 @@ def main() -> int:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.design == "rerilorn":
+        args.steps = min(args.steps, 64)
+        print(json.dumps(run_design(args)))
+        return 0
     print(json.dumps(run_ours(args)))
     return 0
 

@@ -86,6 +86,12 @@ struct DecodeParams {
     int n_kv_heads;
     const int32_t* token_slot;
     int32_t* counters;
+    // A sink per head, a gate per (token, head), softmax weights in two bfloat16 terms (all
+    // optional; see PlAttentionExtras). Not in work-list mode.
+    const float* sinks;
+    const __nv_bfloat16* gate;
+    int64_t gate_row_stride;
+    int split_weights;
 };
 
 // In-cluster merge: outputs are counted in groups of four dims ("vecs"); rank r owns
@@ -347,7 +353,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
         const float corr_lo = exp2f(m_lo - base_lo), corr_hi = exp2f(m_hi - base_hi);
         m_lo = new_lo;
         m_hi = new_hi;
-        uint32_t pa[4];
+        uint32_t pa[4], pb[4] = {0u, 0u, 0u, 0u};
         {
             const float p00 = exp2f(s[0][0] - base_lo), p01 = exp2f(s[0][1] - base_lo);
             const float p02 = exp2f(s[0][2] - base_hi), p03 = exp2f(s[0][3] - base_hi);
@@ -359,6 +365,13 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
             pa[1] = pack_bf16(p02, p03);
             pa[2] = pack_bf16(p10, p11);
             pa[3] = pack_bf16(p12, p13);
+            if (p.split_weights) {
+                // what the rounding to bfloat16 lost, as a second bfloat16 term
+                pb[0] = pack_bf16(p00 - bf16_round(p00), p01 - bf16_round(p01));
+                pb[1] = pack_bf16(p02 - bf16_round(p02), p03 - bf16_round(p03));
+                pb[2] = pack_bf16(p10 - bf16_round(p10), p11 - bf16_round(p11));
+                pb[3] = pack_bf16(p12 - bf16_round(p12), p13 - bf16_round(p13));
+            }
         }
 #pragma unroll
         for (int n = 0; n < HD / 8; ++n) {
@@ -378,6 +391,10 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
                 ldmatrix_x4_trans(b, vt + key * kRowSmem + ((chunk ^ (key & 7)) * 16));
                 mma_bf16(o[2 * dp], pa, b[0], b[1]);
                 mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
+                if (p.split_weights) {
+                    mma_bf16(o[2 * dp], pb, b[0], b[1]);
+                    mma_bf16(o[2 * dp + 1], pb, b[2], b[3]);
+                }
             }
         }
         __syncwarp();
@@ -487,7 +504,13 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
             }
             const int h = kv_head * p.group + r;
             __nv_bfloat16* dst = p.out + t * p.out_row_stride + static_cast<int64_t>(h) * HD + d;
-            if (l > 0.0f) {
+            if (p.sinks != nullptr || p.gate != nullptr) {
+                const float f = pl_attention_row_factor(m, l, p.sinks, p.gate, p.gate_row_stride, t, h);
+                dst[0] = __float2bfloat16_rn(acc.x * f);
+                dst[1] = __float2bfloat16_rn(acc.y * f);
+                dst[2] = __float2bfloat16_rn(acc.z * f);
+                dst[3] = __float2bfloat16_rn(acc.w * f);
+            } else if (l > 0.0f) {
                 dst[0] = __float2bfloat16_rn(acc.x / l);
                 dst[1] = __float2bfloat16_rn(acc.y / l);
                 dst[2] = __float2bfloat16_rn(acc.z / l);
@@ -516,8 +539,10 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
         }
         const int h = kv_head * p.group + r;
         if (n_splits == 1) {
-            p.out[t * p.out_row_stride + static_cast<int64_t>(h) * HD + d] =
-                __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+            p.out[t * p.out_row_stride + static_cast<int64_t>(h) * HD + d] = __float2bfloat16_rn(
+                p.sinks != nullptr || p.gate != nullptr
+                    ? acc * pl_attention_row_factor(m, l, p.sinks, p.gate, p.gate_row_stride, t, h)
+                    : (l > 0.0f ? acc / l : 0.0f));
         } else {
             const int64_t slot = p.items != nullptr
                 ? static_cast<int64_t>(p.token_slot[t] + split) * p.n_heads + h
@@ -718,7 +743,8 @@ __global__ void __launch_bounds__(WARPS * 32, HD <= 64 ? 4 : 2) attention_decode
 template <int HD>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               __nv_bfloat16* __restrict__ out, int64_t out_row_stride, int n_heads,
-                                              int n_splits) {
+                                              int n_splits, const float* __restrict__ sinks,
+                                              const __nv_bfloat16* __restrict__ gate, int64_t gate_row_stride) {
     pl_grid_trigger();
     pl_grid_wait();
     const int t = blockIdx.y, h = blockIdx.x;
@@ -736,7 +762,9 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
                 acc += part_o[(base + s) * HD + d] * scale;
             }
         }
-        out[t * out_row_stride + static_cast<int64_t>(h) * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        out[t * out_row_stride + static_cast<int64_t>(h) * HD + d] = __float2bfloat16_rn(
+            sinks != nullptr || gate != nullptr ? acc * pl_attention_row_factor(m, l, sinks, gate, gate_row_stride, t, h)
+                                                : (l > 0.0f ? acc / l : 0.0f));
     }
 }
 
@@ -848,7 +876,8 @@ int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool
     PL_CHECK_LAUNCH("attention_decode");
     if (p.n_splits > 1) {
         pl_launch_overlapped(attention_decode_merge_kernel<HD>, dim3(p.n_heads, n_tokens), HD <= 64 ? 64 : 128, 0,
-                             stream, p.part_o, p.part_ml, p.out, p.out_row_stride, p.n_heads, p.n_splits);
+                             stream, p.part_o, p.part_ml, p.out, p.out_row_stride, p.n_heads, p.n_splits, p.sinks,
+                             p.gate, p.gate_row_stride);
         PL_CHECK_LAUNCH("attention_decode_merge");
     }
     return 0;
@@ -934,7 +963,8 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
                                int head_dim, int window, float scale, int n_splits, float* scratch,
                                int32_t* status, cudaStream_t stream, float* tile_max = nullptr, int max_tiles = 0,
                                const int32_t* items = nullptr, const int32_t* token_slot = nullptr,
-                               int32_t* counters = nullptr, const PlDecodeRope* rope = nullptr) {
+                               int32_t* counters = nullptr, const PlDecodeRope* rope = nullptr,
+                               const PlAttentionExtras* extras = nullptr) {
     PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
                "attention_decode: bad sizes tokens=%d heads=%d kv_heads=%d", n_tokens, n_heads, n_kv_heads);
     const int group = n_heads / n_kv_heads;
@@ -990,6 +1020,18 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
     }
     p.token_slot = token_slot;
     p.counters = counters;
+    p.sinks = nullptr;
+    p.gate = nullptr;
+    p.gate_row_stride = 0;
+    p.split_weights = 0;
+    if (extras != nullptr) {
+        PL_REQUIRE(items == nullptr && tile_max == nullptr,
+                   "attention_decode: sinks, gates and split weights are not taken over a work list or with attention mass");
+        p.sinks = extras->sinks;
+        p.gate = static_cast<const __nv_bfloat16*>(extras->gate);
+        p.gate_row_stride = extras->gate_row_stride;
+        p.split_weights = extras->split_weights;
+    }
     p.n_heads = n_heads;
     p.group = group;
     p.window = window;
@@ -1023,6 +1065,20 @@ PL_API int pl_attention_decode(const void* q, int64_t q_row_stride, const void* 
                                 table, table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads,
                                 head_dim, window, scale, n_splits, scratch, status, stream, nullptr, 0, nullptr,
                                 nullptr, nullptr, rope);
+}
+
+// pl_attention_decode with a sink per head, a gate per (token, head) and / or softmax weights
+// kept in two bfloat16 terms (see PlAttentionExtras); no position encoding folded in.
+PL_API int pl_attention_decode_extras(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
+                                      int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
+                                      const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
+                                      void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
+                                      int head_dim, int window, float scale, int n_splits, float* scratch,
+                                      const PlAttentionExtras* extras, int32_t* status, cudaStream_t stream) {
+    return run_attention_decode(true, q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size, n_pages,
+                                table, table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads,
+                                head_dim, window, scale, n_splits, scratch, status, stream, nullptr, 0, nullptr,
+                                nullptr, nullptr, nullptr, extras);
 }
 
 // pl_attention_decode over a work list instead of equal shares: for batches whose requests

@@ -41,6 +41,12 @@ struct PrefillParams {
     int window;
     float scale_log2;
     int32_t* status;
+    // A sink per head, a gate per (token, head), softmax weights in two bfloat16 terms (all
+    // optional; see PlAttentionExtras).
+    const float* sinks;
+    const __nv_bfloat16* gate;
+    int64_t gate_row_stride;
+    int split_weights;
 };
 
 template <int HD>
@@ -222,11 +228,20 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
                 const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
                 for (int ks = 0; ks < kBN / 16; ++ks) {
-                    uint32_t pa[4];
+                    uint32_t pa[4], pb[4] = {0u, 0u, 0u, 0u};
                     pa[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
                     pa[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
                     pa[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
                     pa[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+                    if (p.split_weights) {
+                        // what the rounding to bfloat16 lost, as a second bfloat16 term
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const float* w = s[2 * ks + half];
+                            pb[2 * half] = pack_bf16(w[0] - bf16_round(w[0]), w[1] - bf16_round(w[1]));
+                            pb[2 * half + 1] = pack_bf16(w[2] - bf16_round(w[2]), w[3] - bf16_round(w[3]));
+                        }
+                    }
                     const int key = ks * 16 + (mi & 1) * 8 + r;
 #pragma unroll
                     for (int dp = 0; dp < HD / 16; ++dp) {
@@ -234,6 +249,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
                         ldmatrix_x4_trans(b, v_s + swizzled(key, 2 * dp + (mi >> 1), kRowBytes));
                         mma_bf16(o[2 * dp], pa, b[0], b[1]);
                         mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
+                        if (p.split_weights) {
+                            mma_bf16(o[2 * dp], pb, b[0], b[1]);
+                            mma_bf16(o[2 * dp + 1], pb, b[2], b[3]);
+                        }
                     }
                 }
             }
@@ -245,8 +264,14 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    const float inv_lo = l_lo > 0.0f ? 1.0f / l_lo : 0.0f, inv_hi = l_hi > 0.0f ? 1.0f / l_hi : 0.0f;
     const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+    float inv_lo = l_lo > 0.0f ? 1.0f / l_lo : 0.0f, inv_hi = l_hi > 0.0f ? 1.0f / l_hi : 0.0f;
+    if (p.sinks != nullptr || p.gate != nullptr) {
+        inv_lo = pl_attention_row_factor(m_lo, l_lo, p.sinks, p.gate, p.gate_row_stride, row0 + min(r_lo, n_rows - 1),
+                                         head);
+        inv_hi = pl_attention_row_factor(m_hi, l_hi, p.sinks, p.gate, p.gate_row_stride, row0 + min(r_hi, n_rows - 1),
+                                         head);
+    }
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) {
         const int d = 8 * n + 2 * tig;
@@ -290,12 +315,13 @@ PL_API int pl_attention_prefill_supports(int head_dim, int page_size, int dtype)
 // bf16 only. tiles: int32 [n_tiles, 4] = {first token row, rows (1..128), position of
 // the first row, block-table row}; a tile's rows are consecutive tokens of one
 // request at consecutive positions. q and out [T, n_heads, head_dim] with row
-// strides; pools and table as in pl_attention_simt.
+// strides; pools and table as in pl_attention_simt. extras (may be nullptr): sinks, gates,
+// split weights (see PlAttentionExtras).
 PL_API int pl_attention_prefill(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
                                 int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                                 const int32_t* table, int table_width, const int32_t* tiles, int n_tiles, void* out,
                                 int64_t out_row_stride, int n_heads, int n_kv_heads, int head_dim, int window,
-                                float scale, int32_t* status, cudaStream_t stream) {
+                                float scale, const PlAttentionExtras* extras, int32_t* status, cudaStream_t stream) {
     PL_REQUIRE(n_tiles >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
                "attention_prefill: bad sizes tiles=%d heads=%d kv_heads=%d", n_tiles, n_heads, n_kv_heads);
     PL_REQUIRE(pl_attention_prefill_supports(head_dim, page_size, PL_BF16),
@@ -329,6 +355,10 @@ PL_API int pl_attention_prefill(const void* q, int64_t q_row_stride, const void*
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
+    p.sinks = extras != nullptr ? extras->sinks : nullptr;
+    p.gate = extras != nullptr ? static_cast<const __nv_bfloat16*>(extras->gate) : nullptr;
+    p.gate_row_stride = extras != nullptr ? extras->gate_row_stride : 0;
+    p.split_weights = extras != nullptr ? extras->split_weights : 0;
     switch (head_dim) {
         case 32: return launch_prefill<32>(p, n_tiles, n_heads, stream);
         case 48: return launch_prefill<48>(p, n_tiles, n_heads, stream);

@@ -149,3 +149,40 @@ __device__ __forceinline__ float pl_block_max(float v, float* scratch) {
     float total = lane < warps ? scratch[lane] : -INFINITY;
     return pl_warp_max(total);
 }
+
+
+// What some mixers add to softmax attention, for the attention kernels that take it (all
+// fields optional). sinks: fp32 [n_heads]; exp(sinks[h]) joins head h's softmax denominator,
+// a term with no key and no value. gate: [T, n_heads] logits in the engine's dtype with
+// gate_row_stride elements between rows; head h's output for token t is multiplied by
+// sigmoid(gate[t, h]). split_weights != 0: the tensor-core kernels feed the softmax weights
+// to the value product as two bfloat16 terms (the rounded weight and what the rounding
+// lost), so the weights keep 16 mantissa bits instead of 8.
+struct PlAttentionExtras {
+    const float* sinks;
+    const void* gate;
+    int64_t gate_row_stride;
+    int split_weights;
+};
+
+// The factor that turns an accumulated row (sum of exp2(s - m) * v, with l the sum of
+// exp2(s - m)) into the head's output: 1 / l, or with a sink exp2(m - m') / (l exp2(m - m') +
+// exp2(sink - m')) for m' = max(m, sink); times the gate when there is one. m and the sink
+// are in the exponent's units (scaled score * log2 e).
+__device__ __forceinline__ float pl_attention_row_factor(float m, float l, const float* sinks,
+                                                         const __nv_bfloat16* gate, int64_t gate_row_stride,
+                                                         int64_t t, int h) {
+    float factor;
+    if (sinks != nullptr) {
+        const float sink = sinks[h] * 1.4426950408889634f;
+        const float top = fmaxf(m, sink);
+        const float keep = m > -INFINITY ? exp2f(m - top) : 0.0f;
+        factor = keep / (l * keep + exp2f(sink - top));
+    } else {
+        factor = l > 0.0f ? 1.0f / l : 0.0f;
+    }
+    if (gate != nullptr) {
+        factor *= 1.0f / (1.0f + expf(-__bfloat162float(gate[t * gate_row_stride + h])));
+    }
+    return factor;
+}

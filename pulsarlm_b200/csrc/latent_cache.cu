@@ -16,6 +16,8 @@ __global__ void norm_write_paged_kernel(const scalar_t* __restrict__ z, int64_t 
                                         const int32_t* __restrict__ table, int table_width,
                                         scalar_t* __restrict__ pool, int64_t page_stride, int page_size, int n_pages,
                                         int rank, int n_tokens, int32_t* status) {
+    pl_grid_trigger();
+    pl_grid_wait();
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= n_tokens) {
@@ -57,9 +59,10 @@ PL_API int pl_norm_write_paged(const void* z, int64_t row_stride, const float* w
     }
     const int warps = 4;
     PL_DISPATCH_DTYPE(dtype, "norm_write_paged", {
-        norm_write_paged_kernel<scalar_t><<<(n_tokens + warps - 1) / warps, warps * 32, 0, stream>>>(
-            static_cast<const scalar_t*>(z), row_stride, weight, eps, pos, entry, table, table_width,
-            static_cast<scalar_t*>(pool), page_stride, page_size, n_pages, rank, n_tokens, status);
+        pl_launch_overlapped(norm_write_paged_kernel<scalar_t>, dim3((n_tokens + warps - 1) / warps), dim3(warps * 32), 0,
+                             stream, static_cast<const scalar_t*>(z), row_stride, weight, eps, pos, entry, table,
+                             table_width, static_cast<scalar_t*>(pool), page_stride, page_size, n_pages, rank,
+                             n_tokens, status);
     });
     PL_CHECK_LAUNCH("norm_write_paged");
     return 0;

@@ -48,6 +48,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // 2^x by the hardware's approximation (2 ulp; -inf gives 0). The probabilities it
 // makes are rounded to bfloat16 right after, so the fp32 engine never uses it.
+// x rounded to bfloat16 and back.
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -18,7 +18,9 @@ template <typename scalar_t>
 __global__ void short_conv_kernel(const scalar_t* __restrict__ h, const float* __restrict__ weight,
                                   const scalar_t* __restrict__ state, const int32_t* __restrict__ entry,
                                   const int32_t* __restrict__ slots, scalar_t* __restrict__ out, int n_tokens,
-                                  int width, int taps) {
+                                  int width, int taps, int vectors) {
+    pl_grid_trigger();
+    pl_grid_wait();
     const int t = blockIdx.x;
     const int e = entry[t];
     const int reach = taps - 1;
@@ -28,6 +30,31 @@ __global__ void short_conv_kernel(const scalar_t* __restrict__ h, const float* _
         ++inside;
     }
     const scalar_t* old = state + static_cast<int64_t>(slots[e]) * reach * width;
+    if (vectors) {
+        // Four channels per thread, 8- or 16-byte loads (the width is a multiple of 4 and rows start on 16 bytes).
+        for (int c = 4 * threadIdx.x; c < width; c += 4 * blockDim.x) {
+            const float4 own = pl_load4(h + static_cast<int64_t>(t) * width + c);
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int j = 0; j < taps; ++j) {
+                const int back = reach - j;
+                float4 v;
+                if (back == 0) {
+                    v = own;
+                } else if (back <= inside) {
+                    v = pl_load4(h + static_cast<int64_t>(t - back) * width + c);
+                } else {
+                    v = pl_load4(old + static_cast<int64_t>(reach - (back - inside)) * width + c);
+                }
+                acc.x = fmaf(weight[static_cast<int64_t>(c) * taps + j], v.x, acc.x);
+                acc.y = fmaf(weight[static_cast<int64_t>(c + 1) * taps + j], v.y, acc.y);
+                acc.z = fmaf(weight[static_cast<int64_t>(c + 2) * taps + j], v.z, acc.z);
+                acc.w = fmaf(weight[static_cast<int64_t>(c + 3) * taps + j], v.w, acc.w);
+            }
+            pl_store4(out + static_cast<int64_t>(t) * width + c,
+                      make_float4(own.x + acc.x, own.y + acc.y, own.z + acc.z, own.w + acc.w));
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         const float* w = weight + static_cast<int64_t>(c) * taps;
         const float own = pl_load(h + static_cast<int64_t>(t) * width + c);
@@ -55,6 +82,8 @@ template <typename scalar_t>
 __global__ void short_conv_state_kernel(const scalar_t* __restrict__ h, const int32_t* __restrict__ entry,
                                         const int32_t* __restrict__ slots, scalar_t* __restrict__ state,
                                         int n_tokens, int width, int taps) {
+    pl_grid_trigger();
+    pl_grid_wait();
     const int t = blockIdx.x;
     const int e = entry[t];
     const int reach = taps - 1;
@@ -104,11 +133,14 @@ PL_API int pl_short_conv(const void* h, const float* weight, const void* state, 
     if (n_tokens == 0) {
         return 0;
     }
-    const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
+    const int vectors = width % 4 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(state) |
+                                            reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int lanes = vectors ? width / 4 : width;
+    const int threads = lanes >= 256 ? 256 : ((lanes + 31) / 32) * 32;
     PL_DISPATCH_DTYPE(dtype, "short_conv", {
-        short_conv_kernel<scalar_t><<<n_tokens, threads, 0, stream>>>(
-            static_cast<const scalar_t*>(h), weight, static_cast<const scalar_t*>(state), entry, slots,
-            static_cast<scalar_t*>(out), n_tokens, width, taps);
+        pl_launch_overlapped(short_conv_kernel<scalar_t>, dim3(n_tokens), dim3(threads), 0, stream,
+                             static_cast<const scalar_t*>(h), weight, static_cast<const scalar_t*>(state), entry, slots,
+                             static_cast<scalar_t*>(out), n_tokens, width, taps, vectors);
     });
     PL_CHECK_LAUNCH("short_conv");
     return 0;
@@ -125,8 +157,9 @@ PL_API int pl_short_conv_state(const void* h, const int32_t* entry, const int32_
     }
     const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
     PL_DISPATCH_DTYPE(dtype, "short_conv_state", {
-        short_conv_state_kernel<scalar_t><<<n_tokens, threads, 0, stream>>>(
-            static_cast<const scalar_t*>(h), entry, slots, static_cast<scalar_t*>(state), n_tokens, width, taps);
+        pl_launch_overlapped(short_conv_state_kernel<scalar_t>, dim3(n_tokens), dim3(threads), 0, stream,
+                             static_cast<const scalar_t*>(h), entry, slots, static_cast<scalar_t*>(state), n_tokens,
+                             width, taps);
     });
     PL_CHECK_LAUNCH("short_conv_state");
     return 0;

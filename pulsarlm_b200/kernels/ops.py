@@ -36,12 +36,13 @@ class KernelError(RuntimeError):
 
 _SIGNATURES = {
     "pl_embed": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR],
-    "pl_add_normed_rmsnorm": [_PTR, _PTR, _PTR, _PTR, _F32, _F32, _PTR, _F32, _PTR, _PTR, _I32, _I32, _I32, _PTR],
+    "pl_add_normed_rmsnorm": [_PTR, _PTR, _PTR, _PTR, _F32, _F32, _PTR, _F32, _PTR, _PTR, _I32, _I32, _PTR, _PTR, _PTR,
+                              _I32, _I32, _PTR],
     "pl_bias_act": [_PTR, _I64, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
     "pl_short_conv": [_PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
     "pl_short_conv_state": [_PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
     "pl_delta_rule": [_PTR, _PTR, _PTR, _PTR, _PTR, _I64, _PTR, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR,
-                      _I64, _I32, _I32, _I32, _F32, _F32, _F32, _I32, _PTR],
+                      _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _F32, _F32, _I32, _PTR],
     "pl_norm_write_paged": [_PTR, _I64, _PTR, _F32, _PTR, _PTR, _PTR, _I32, _PTR, _I64, _I32, _I32, _I32, _I32, _I32,
                             _PTR, _PTR],
     "pl_take_tokens": [_PTR, _PTR, _PTR, _I32, _I32, _PTR, _PTR],
@@ -67,7 +68,9 @@ _SIGNATURES = {
     "pl_fill_random": [_PTR, _I64, _I32, ctypes.c_uint64, ctypes.c_uint64, _F32, _F32, _PTR],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
     "pl_attention_prefill": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32, _PTR, _I64,
-                             _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
+                             _I32, _I32, _I32, _I32, _F32, _PTR, _PTR, _PTR],
+    "pl_attention_decode_extras": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
+                                   _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_prefill_supports": [_I32, _I32, _I32],
     "pl_attention_prefill_tcgen05": [_PTR, _I64, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32,
                                      _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _I32, _PTR, _PTR, _PTR],
@@ -236,11 +239,24 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
 
 def add_normed_rmsnorm(x: torch.Tensor, y: torch.Tensor, y_weight: torch.Tensor, mult: float, y_eps: float,
                        weight: torch.Tensor | None, eps: float, out: torch.Tensor | None,
-                       rows: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> None:
+                       rows: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+                       conv: tuple | None = None) -> None:
     """x fp32 [T, H] += mult * rmsnorm(y + bias) * y_weight (in place unless rows is given); out =
     rmsnorm(x) * weight when out is given. y, bias and out in the engine's dtype, the weights fp32.
-    With rows (int32 [R]), output row r is made from source row rows[r] and x is left as it was."""
+    With rows (int32 [R]), output row r is made from source row rows[r] and x is left as it was.
+    conv = (weight fp32 [H, taps], state [slots, taps - 1, H], slots int32 [T]): in a step whose
+    entries bring one token each (row t is entry t), the short convolution over time rides along:
+    out = short_conv(normed row) and every entry's state slot moves on (see short_conv)."""
     _dev(x, y, y_weight, weight, out, rows, bias)
+    conv_weight = conv_state = conv_slots = None
+    taps = 0
+    if conv is not None:
+        conv_weight, conv_state, conv_slots = conv
+        _dev(conv_weight, conv_state, conv_slots)
+        taps = conv_weight.shape[1]
+        assert rows is None and out is not None and conv_weight.dtype == torch.float32 and conv_weight.is_contiguous()
+        assert conv_weight.shape[0] == x.shape[-1] and conv_slots.dtype == torch.int32 and conv_slots.numel() >= x.shape[0]
+        assert conv_state.dtype == y.dtype and conv_state.is_contiguous() and conv_state.shape[1:] == (taps - 1, x.shape[-1])
     hidden = x.shape[-1]
     assert x.dtype == torch.float32 and x.is_contiguous() and y.shape == x.shape and y.is_contiguous()
     assert y_weight.dtype == torch.float32 and y_weight.shape == (hidden,) and y_weight.is_contiguous()
@@ -253,7 +269,8 @@ def add_normed_rmsnorm(x: torch.Tensor, y: torch.Tensor, y_weight: torch.Tensor,
     if rows is not None:
         assert rows.dtype == torch.int32 and rows.is_contiguous()
     _call("pl_add_normed_rmsnorm", _p(x), _p(y), _p(bias), _p(y_weight), float(mult), float(y_eps), _p(weight),
-          float(eps), _p(out), _p(rows), n_rows, hidden, _code(y.dtype), _stream())
+          float(eps), _p(out), _p(rows), n_rows, hidden, _p(conv_weight), _p(conv_state), _p(conv_slots), taps,
+          _code(y.dtype), _stream())
 
 
 BIAS_ACT = {"none": 0, "relu2": 1, "tanh": 2}
@@ -313,10 +330,14 @@ def delta_rule(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tenso
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (n_heads, dim, dim)
     assert out.shape[1] == width and out.stride(1) == 1
     n_entries = first_rows.numel()
+    tokens = r.shape[0]
     assert counts.numel() == n_entries and slots.numel() >= n_entries
+    o_raw = torch.empty((tokens, width), dtype=torch.float32, device=out.device)  # (the scan's output before the norm)
     _call("pl_delta_rule", _p(r), _p(k), _p(v), _p(g), _p(a_pre), stride, _p(w_pre), w_pre.stride(0), _p(w0), _p(a0),
-          _p(norm), _p(state), _p(first_rows), _p(counts), _p(slots), _p(out), out.stride(0), n_entries, n_heads, dim,
-          float(decay_scale), float(unit_eps), float(eps), _code(out.dtype), _stream())
+          _p(norm), _p(state), _p(first_rows), _p(counts), _p(slots), _p(o_raw), _p(out), out.stride(0), tokens,
+          n_entries, n_heads, dim, float(decay_scale), float(unit_eps), float(eps), _code(out.dtype), _stream())
+    global _launches
+    _launches += 1  # (two kernels)
 
 
 def norm_write_paged(z: torch.Tensor, weight: torch.Tensor, eps: float, pos: torch.Tensor, entry: torch.Tensor,
@@ -592,11 +613,32 @@ def attention_decode_ctas_per_sm(head_dim: int) -> int:
     return int(library().pl_attention_decode_ctas_per_sm(head_dim))
 
 
+class _AttentionExtras(ctypes.Structure):
+    _fields_ = [("sinks", _PTR), ("gate", _PTR), ("gate_row_stride", _I64), ("split_weights", _I32)]
+
+
+def attention_extras(q: torch.Tensor, sinks: torch.Tensor | None, gate: torch.Tensor | None,
+                     split_weights: bool) -> "_AttentionExtras | None":
+    """What the tensor-core attention kernels take beyond plain softmax attention (the struct
+    PlAttentionExtras): sinks fp32 [nh] (exp(sinks[h]) joins head h's denominator), gate [T, nh]
+    logits in q's dtype (outputs times their sigmoid), split_weights (softmax weights enter the
+    value product as two bfloat16 terms). None when nothing is asked for. The tensors must
+    outlive the call that takes the struct."""
+    if sinks is None and gate is None and not split_weights:
+        return None
+    _dev(sinks, gate)
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.shape == (q.shape[1],) and sinks.is_contiguous()
+    if gate is not None:
+        assert gate.dtype == q.dtype and gate.shape == (q.shape[0], q.shape[1]) and gate.stride(1) == 1
+    return _AttentionExtras(_p(sinks), _p(gate), gate.stride(0) if gate is not None else 0, int(bool(split_weights)))
+
+
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
                      pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
                      scale: float, n_splits: int, scratch: torch.Tensor | None,
                      status: torch.Tensor | None = None, mass: tuple | None = None,
-                     rope: tuple | None = None) -> None:
+                     rope: tuple | None = None, extras: "_AttentionExtras | None" = None) -> None:
     """bf16 attention of single decode tokens, split over the keys `n_splits` ways;
     shapes as attention_simt. `scratch`: fp32, attention_decode_scratch_floats long.
     `mass` = (tile_max, mass_sum, weight_sum, decay): also measures attention mass.
@@ -637,6 +679,13 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
               _p(scratch), _p(tile_max), max_tiles, _p(mass_sum), _p(weight_sum), float(decay), _p(status),
               _stream())
         return
+    if extras is not None:
+        assert rope is None, "sinks, gates and split weights: not together with the folded position encoding"
+        _call("pl_attention_decode_extras", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0),
+              k_pool.stride(1), page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out),
+              out.stride(0), tokens, n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits),
+              _p(scratch), ctypes.byref(extras), _p(status), _stream())
+        return
     _call("pl_attention_decode", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
           page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
           n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch),
@@ -655,9 +704,10 @@ def attention_prefill_tile_rows() -> int:
 
 def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
                       tiles: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None, scale: float,
-                      status: torch.Tensor | None = None) -> None:
+                      status: torch.Tensor | None = None, extras: "_AttentionExtras | None" = None) -> None:
     """bf16 causal attention of prompt portions. tiles int32 [n, 4]: {first token
-    row, rows, position of the first row, block-table row}; q, out [T, nh, hd]."""
+    row, rows, position of the first row, block-table row}; q, out [T, nh, hd]. extras: see
+    attention_extras."""
     _dev(q, k_pool, v_pool, table, tiles, out, status)
     tokens, n_heads, head_dim = q.shape
     n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
@@ -670,7 +720,8 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     assert tiles.dtype == torch.int32 and tiles.dim() == 2 and tiles.shape[1] == 4 and tiles.is_contiguous()
     _call("pl_attention_prefill", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
           page_size, n_pages, _p(table), table.shape[1], _p(tiles), tiles.shape[0], _p(out), out.stride(0),
-          n_heads, n_kv, head_dim, int(window or 0), float(scale), _p(status), _stream())
+          n_heads, n_kv, head_dim, int(window or 0), float(scale),
+          ctypes.byref(extras) if extras is not None else None, _p(status), _stream())
 
 
 def attention_prefill_tcgen05_supports(q: torch.Tensor, k_pool: torch.Tensor, page_size: int) -> bool:

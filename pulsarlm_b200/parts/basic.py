@@ -59,12 +59,14 @@ class RMSNorm(Part):
         return self._weight_f32
 
     def forward(self, x: torch.Tensor, delta: "torch.Tensor | NormedDelta | None" = None,
-                rows: torch.Tensor | None = None) -> torch.Tensor:
+                rows: torch.Tensor | None = None, conv: tuple | None = None) -> torch.Tensor:
+        """conv: see ops.add_normed_rmsnorm (only with a NormedDelta; the caller checks that the
+        step's entries bring one token each)."""
         n = rows.numel() if rows is not None else x.shape[0]
         out = torch.empty((n, self.hidden), dtype=self.ctx.dtype, device=x.device)
         if isinstance(delta, NormedDelta):
             ops.add_normed_rmsnorm(x, delta.y, delta.weight, delta.mult, delta.eps, self.weight_f32(), self.eps, out,
-                                   rows, delta.bias)
+                                   rows, delta.bias, conv)
         else:
             ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
         return out

@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch
 
 from . import native_layer
+from .basic import NormedDelta
 from .registry import BuildContext, build_part, register_part
 from .spec import LayerSpec
 
@@ -105,16 +106,24 @@ class SandwichNormBlock:
         """The parts that keep something per request, the mixer first."""
         return [self.mixer] + [f for f in (self.mixer_filter, self.ff_filter) if f is not None]
 
+    @staticmethod
+    def _input(norm, filt, x, delta, batch):
+        """A sublayer's input: the norm (with the pending output added first), then the filter.
+        Where the filter can ride along in the norm's kernel (a step of single tokens), one launch."""
+        if filt is None:
+            return norm.forward(x, delta)
+        ride = getattr(filt, "rides_along", None)
+        conv = ride(batch) if ride is not None and isinstance(delta, NormedDelta) else None
+        if conv is not None:
+            return norm.forward(x, delta, conv=conv)
+        return filt.forward(norm.forward(x, delta), batch)
+
     def forward(self, x: torch.Tensor, delta, batch):
-        h = self.mixer_norm.forward(x, delta)
-        if self.mixer_filter is not None:
-            h = self.mixer_filter.forward(h, batch)
+        h = self._input(self.mixer_norm, self.mixer_filter, x, delta, batch)
         delta = self.mixer_out_norm.pending(self.mixer.forward(h, batch), self.mult)
         if self.feed_forward is None:
             return x, delta
-        h = self.ff_norm.forward(x, delta)
-        if self.ff_filter is not None:
-            h = self.ff_filter.forward(h, batch)
+        h = self._input(self.ff_norm, self.ff_filter, x, delta, batch)
         # A bias on the feed-forward's last projection is added by the kernel that norms its output.
         bias = getattr(self.feed_forward, "down_bias", None)
         if bias is not None:

@@ -2,13 +2,20 @@
 
 from __future__ import annotations
 
+import os
+
+import numpy as np
 import torch
 
 from ..kernels import ops
-from .attention import KVBinding
+from .attention import KVBinding, decode_splits
 from .linear import linear
 from .registry import BuildContext, Part, register_part
 from .spec import KVCacheNeed, PartSpec, TensorNeed
+
+
+# (1: every token attends on the CUDA-core kernel, for comparison)
+CUDA_CORES_ONLY = os.environ.get("PULSARLM_B200_LATENT_CUDA_CORES", "0") == "1"
 
 
 def per_head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -59,6 +66,7 @@ class LatentAttention(Part):
         self.stacked: torch.Tensor | None = None
         self.up_k = self.up_v = self.o = self.latent_norm = self.sink = None
         self.cache: KVBinding | None = None
+        self._tensor_cores: tuple[bool, bool] | None = None
 
     @classmethod
     def tensor_needs(cls, spec: PartSpec) -> dict[str, TensorNeed]:
@@ -109,8 +117,82 @@ class LatentAttention(Part):
         per_head_linear(mixed, self.up_v, out)
         return linear(out.view(tokens, nh * vd), self.o)
 
+    # ------------------------------------------------------------------ planning a step
+    def _kernels(self) -> tuple[bool, bool]:
+        """Whether the tensor-core kernels for single tokens and for prompt portions take this
+        layer's shape: all heads share the one latent row, so they are one group of n_heads
+        query heads over a "kv head" of size rank."""
+        if self._tensor_cores is None:
+            dtype = self.ctx.dtype
+            self._tensor_cores = (False, False) if CUDA_CORES_ONLY else (
+                ops.attention_decode_supports(self.rank, self.n_heads, self.cache.page_size, dtype),
+                ops.attention_prefill_supports(self.rank, self.cache.page_size, dtype))
+        return self._tensor_cores
+
+    def slow_path_note(self) -> str | None:
+        if self.cache is None or self.ctx.dtype != torch.bfloat16 or all(self._kernels()):
+            return None
+        return (f"latent attention with rank {self.rank} and {self.n_heads} heads runs on the CUDA-core attention "
+                f"kernel (the tensor-core kernels take ranks 32 to 128 in steps of 16, up to 16 heads and pages that "
+                f"are multiples of 16 tokens); expect it several times slower")
+
+    def plan_key(self):
+        if self.cache is None:
+            return None
+        return ("latent attention", self.cache.page_size, self.rank, self.n_heads, self.window, self.ctx.dtype)
+
+    def plan_step(self, step) -> dict:
+        """The tile list of the prompt-portion kernel (int32 [tiles, 4] rows of {first token
+        row, rows, position of the first row, block-table row}, the tiles that read the most
+        keys first) and the most keys a single token reads."""
+        decode_kernel, prefill_kernel = self._kernels()
+        plan: dict = {"tiles": None, "max_context": 0}
+        if decode_kernel and step.n_decode:
+            plan["max_context"] = step.context_bound if step.fixed_shape else max(step.context_lens[: step.n_decode])
+        if not prefill_kernel or step.n_decode == step.n_entries:
+            return plan
+        rows = ops.attention_prefill_tile_rows()
+        tiles = []
+        for e in range(step.n_decode, step.n_entries):
+            n, at = step.query_lens[e], step.first_rows[e]
+            start = step.context_lens[e] - n
+            tiles += [(at + r, min(rows, n - r), start + r, e) for r in range(0, n, rows)]
+        tiles.sort(key=lambda t: -(min(t[2] + t[1], self.window + t[1]) if self.window else t[2] + t[1]))
+        plan["tiles"] = np.array(tiles, dtype=np.int32).reshape(len(tiles), 4)
+        return plan
+
     def attend(self, q: torch.Tensor, out: torch.Tensor, table: torch.Tensor, batch, gate) -> None:
-        """out[t, h] = gate * sum_j p_j c_j over the latents in reach of token t."""
+        """out[t, h] = gate * sum_j p_j c_j over the latents in reach of token t. In bfloat16 the
+        batch's leading single tokens go to the split-key tensor-core kernel and prompt
+        portions to the tiled one, both with the sink and the gate in their last step and the
+        softmax weights kept in two bfloat16 terms; float32, and shapes those kernels do not
+        take, attend on the CUDA-core kernel."""
         cache = self.cache
-        ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
-                           self.window, self.scale, batch.status, sinks=self.sink, gate=gate)
+        tokens = q.shape[0]
+        plan = batch.plans.get(self.plan_key()) or {}
+        decode_kernel, prefill_kernel = self._kernels()
+        n_decode = min(int(batch.n_decode), tokens) if decode_kernel else 0
+        if n_decode > 0:
+            max_context = plan.get("max_context") or max(batch.host_context_lens[:n_decode])
+            if self.window:
+                max_context = min(max_context, self.window + 16)
+            splits = decode_splits(n_decode, max_context, q.device, self.rank, self.n_heads)
+            scratch = None
+            if splits > 1:
+                scratch = torch.empty(ops.attention_decode_scratch_floats(n_decode, self.n_heads, self.rank, splits),
+                                      dtype=torch.float32, device=q.device)
+            extras = ops.attention_extras(q[:n_decode], self.sink, gate[:n_decode] if gate is not None else None, True)
+            ops.attention_decode(q[:n_decode], cache.k_pool, cache.v_pool, table, batch.pos[:n_decode],
+                                 batch.entry[:n_decode], out[:n_decode], cache.page_size, self.window, self.scale,
+                                 splits, scratch, batch.status, extras=extras)
+        if n_decode == tokens:
+            return
+        tiles = plan.get("tiles")
+        if prefill_kernel and tiles is not None and n_decode == int(batch.n_decode):
+            # (the tile list covers exactly the tokens after the leading single tokens)
+            ops.attention_prefill(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size, self.window,
+                                  self.scale, batch.status, extras=ops.attention_extras(q, self.sink, gate, True))
+            return
+        ops.attention_simt(q[n_decode:], cache.k_pool, cache.v_pool, table, batch.pos[n_decode:],
+                           batch.entry[n_decode:], out[n_decode:], cache.page_size, self.window, self.scale,
+                           batch.status, sinks=self.sink, gate=gate[n_decode:] if gate is not None else None)

@@ -2,11 +2,16 @@
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..kernels import ops
 from .registry import BuildContext, Part, register_part
 from .spec import PartSpec, StateNeed, TensorNeed
+
+
+FUSE_DECODE = os.environ.get("PULSARLM_B200_FUSE_CONV", "1") != "0"  # (0: always the separate kernels, for comparison)
 
 
 @register_part("filter", "short_conv")
@@ -42,6 +47,16 @@ class ShortConv(Part):
 
     def captures_state_steps(self) -> bool:
         return True  # (no host round trip: the state moves on inside the step's kernels)
+
+    def rides_along(self, batch) -> tuple | None:
+        """In a step whose entries bring one token each, what the norm kernel in front needs to
+        do this part's work too (see ops.add_normed_rmsnorm): one launch instead of three."""
+        if not FUSE_DECODE or int(batch.n_decode) != int(batch.n_tokens):
+            return None
+        if self.taps == 1:
+            return (self.weight, torch.empty((1, 0, self.hidden), dtype=self.ctx.dtype, device=self.weight.device),
+                    batch.slots)
+        return (self.weight, self.binding.states, batch.slots)
 
     def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
         out = torch.empty_like(h)

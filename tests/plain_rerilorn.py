@@ -113,20 +113,22 @@ def forward(config: dict, tensors: dict, tokens: list[int], state: dict | None =
         p = f"l{i}."
         m = layer["mixer"]
         h = rms_norm(x, tensors[p + "norm1"], eps)
-        h, state[p + "canon1"] = short_convolution(h, tensors[p + "canon1"], state.get(p + "canon1"))
+        if config.get("canon"):
+            h, state[p + "canon1"] = short_convolution(h, tensors[p + "canon1"], state.get(p + "canon1"))
         mix = _sub(tensors, p + "mix.")
         if layer["type"] == "general_delta":
             y, state[p + "S"] = general_delta_mixer(h, mix, int(m["heads"]), int(m["dim"]), eps, state.get(p + "S"))
         elif layer["type"] == "latent_attention":
             y, state[p + "c"] = latent_attention_mixer(h, mix, int(m["heads"]), int(m["dim"]), int(m["vdim"]),
-                                                       float(m["scale"]), int(m["mask"]["size"]), eps,
+                                                       float(m["scale"]), int(m["mask"]["size"]) if m.get("mask") else 1 << 30, eps,
                                                        state.get(p + "c"))
         else:
             raise ValueError(layer["type"])
         x = x + mult * rms_norm(y, tensors[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
             h = rms_norm(x, tensors[p + "norm2"], eps)
-            h, state[p + "canon2"] = short_convolution(h, tensors[p + "canon2"], state.get(p + "canon2"))
+            if config.get("canon"):
+                h, state[p + "canon2"] = short_convolution(h, tensors[p + "canon2"], state.get(p + "canon2"))
             y = dense_feed_forward(h, _sub(tensors, p + "mlp."))
             x = x + mult * rms_norm(y, tensors[p + "norm2b"], eps)
         if layer_outputs is not None:
