@@ -10,16 +10,23 @@
 //
 // Two kernels. The scan: a CTA per (batch entry, head, block of value columns) walks the
 // entry's rows in order. Column j of S never meets another column, so each column lives in
-// registers: `parts` lanes of a warp share a column, lane p holding rows p, p + parts, ... .
-// The rows are taken in chunks: while one chunk's tokens update the state one after the
-// other (no block-wide wait inside: only the shuffles among a column's lanes), the next
-// chunk's projections arrive in shared memory (cp.async), and between chunks the warps turn
-// them, a token each, into the fp32 vectors u, w, a * u, k, r that the update reads. The raw
-// o goes to scratch in fp32; the second kernel norms it per head, applies the norm's weight
-// and the gate and rounds once. Everything after the projections is fp32 (they arrive in
-// the engine's dtype). The order of every sum depends on the head size alone, so a token's
-// result depends on the tokens before it only, not on how the prompt was cut, on the chunks
-// or on the rest of the batch.
+// registers: `parts` lanes of a warp share a column and each holds some of its rows. The
+// rows are taken in chunks: while one chunk's tokens update the state one after the other
+// (no block-wide wait inside: only the shuffles among a column's lanes), the next chunk's
+// projections arrive in shared memory (cp.async); between chunks all threads turn them
+// into the fp32 vectors u, w, a * u, k, r that the update reads (the unit-key factor by a
+// warp per token, the rest one (token, channel) per thread, so that the exponentials
+// overlap). Head sizes 16, 32, 64 and 128 run a form with the sizes known to the compiler:
+// a lane holds consecutive rows, reads its share of the vectors one token ahead with
+// 16-byte loads, and leaves its share of o in shared memory, added up after the chunk, off
+// the path from one token to the next. The raw o goes to scratch in fp32; the second kernel
+// norms it per head, applies the norm's weight and the gate and rounds once. Everything
+// after the projections is fp32 (they arrive in the engine's dtype). The order of every sum
+// depends on the head size alone, so a token's result depends on the tokens before it only,
+// not on how the prompt was cut, on the chunks or on the rest of the batch. What bounds the
+// scan is the chain from one token's state to the next (a dot product over a column, the
+// shuffles that add its lanes' shares, the update): a prompt of one request keeps a few SMs
+// busy and takes about a microsecond a token whatever the width.
 #include "common.cuh"
 
 #include "mma_helpers.cuh"
@@ -95,6 +102,41 @@ __device__ __forceinline__ void load_chunk(const ScanParams& p, scalar_t* raw, i
     cp_async_commit();
 }
 
+// The fp32 vectors of the update for one chunk: first each token's unit-key factor (a warp per
+// token), then every (token, channel) on its own, so that the exponentials' latencies overlap.
+// vec: [token][k, u, w, a * u, r][dim]. Ends with the block in step.
+template <typename scalar_t>
+__device__ __forceinline__ void prepare_chunk(const ScanParams& p, const scalar_t* raw, float* vec,
+                                              const float* offsets, float* inv_norm, int n, int dim) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+    for (int c = warp; c < n; c += warps) {
+        const scalar_t* rk = raw + (c * 4 + 1) * dim;
+        float square = 0.0f;
+        for (int i = lane; i < dim; i += 32) {
+            const float kv = pl_load(rk + i);
+            square += kv * kv;
+        }
+        square = pl_warp_sum(square);
+        if (lane == 0) {
+            inv_norm[c] = 1.0f / sqrtf(square + p.unit_eps);
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < n * dim; idx += blockDim.x) {
+        const int c = idx / dim, i = idx - c * dim;
+        const scalar_t* token = raw + c * 4 * dim;
+        const float kv = pl_load(token + dim + i);
+        const float u = kv * inv_norm[c];
+        float* out = vec + c * 5 * dim;
+        out[i] = kv;
+        out[dim + i] = u;
+        out[2 * dim + i] = expf(-p.decay_scale * sigmoid_f32(pl_load(token + 2 * dim + i) + offsets[i]));
+        out[3 * dim + i] = sigmoid_f32(pl_load(token + 3 * dim + i) + offsets[dim + i]) * u;
+        out[4 * dim + i] = pl_load(token + i);
+    }
+    __syncthreads();
+}
+
 template <typename scalar_t>
 __global__ void __launch_bounds__(kMaxThreads) delta_rule_scan_kernel(const ScanParams p) {
     pl_grid_trigger();
@@ -113,7 +155,7 @@ __global__ void __launch_bounds__(kMaxThreads) delta_rule_scan_kernel(const Scan
     const int e = blockIdx.x, head = blockIdx.y;
     const int col0 = blockIdx.z * p.cols;
     const int n_cols = min(p.cols, dim - col0);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+    const int tid = threadIdx.x;
     const int col = tid / parts, part = tid % parts;  // (threads past the last column only wait and shuffle)
     const bool active = col < n_cols;
     const int first = p.first_rows[e], count = p.counts[e];
@@ -145,34 +187,7 @@ __global__ void __launch_bounds__(kMaxThreads) delta_rule_scan_kernel(const Scan
             asm volatile("cp.async.wait_group 0;\n" ::);
         }
         __syncthreads();
-        // The fp32 vectors of the update: first each token's unit-key factor (a warp per token),
-        // then every (token, channel) on its own, so that the exponentials' latencies overlap.
-        for (int c = warp; c < n; c += warps) {
-            const scalar_t* rk = raw + (c * 4 + 1) * dim;
-            float square = 0.0f;
-            for (int i = lane; i < dim; i += 32) {
-                const float kv = pl_load(rk + i);
-                square += kv * kv;
-            }
-            square = pl_warp_sum(square);
-            if (lane == 0) {
-                inv_norm[c] = 1.0f / sqrtf(square + p.unit_eps);
-            }
-        }
-        __syncthreads();
-        for (int idx = tid; idx < n * dim; idx += blockDim.x) {
-            const int c = idx / dim, i = idx - c * dim;
-            const scalar_t* token = raw + c * 4 * dim;
-            const float kv = pl_load(token + dim + i);
-            const float u = kv * inv_norm[c];
-            float* out = vec + c * 5 * dim;
-            out[i] = kv;
-            out[dim + i] = u;
-            out[2 * dim + i] = expf(-p.decay_scale * sigmoid_f32(pl_load(token + 2 * dim + i) + offsets[i]));
-            out[3 * dim + i] = sigmoid_f32(pl_load(token + 3 * dim + i) + offsets[dim + i]) * u;
-            out[4 * dim + i] = pl_load(token + i);
-        }
-        __syncthreads();
+        prepare_chunk<scalar_t>(p, raw, vec, offsets, inv_norm, n, dim);
         // The tokens one after the other; nothing here waits for another warp.
         const scalar_t* raw_v = raw + chunk * 4 * dim;
         for (int c = 0; c < n; ++c) {
@@ -227,6 +242,164 @@ __global__ void __launch_bounds__(kMaxThreads) delta_rule_scan_kernel(const Scan
         if (active && i < dim) {
             mine[static_cast<int64_t>(i) * dim + col0 + col] = S[m];
         }
+    }
+}
+
+// The same scan with the head size and the lanes per column known to the compiler (the common
+// head sizes): a lane holds ROWS consecutive rows of its column, reads its share of the five
+// vectors with 16-byte loads and needs no index arithmetic per row. Its sums run in another
+// order than the kernel above (a head size uses one of the two, always the same).
+template <typename scalar_t, int DIM, int PARTS>
+__global__ void __launch_bounds__(kMaxThreads) delta_rule_scan_static_kernel(const ScanParams p) {
+    constexpr int ROWS = DIM / PARTS;
+    static_assert(ROWS % 4 == 0 && ROWS * PARTS == DIM && PARTS <= 32, "rows per lane: a multiple of four");
+    pl_grid_trigger();
+    pl_grid_wait();
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int chunk = p.chunk;
+    float* offsets = reinterpret_cast<float*>(smem);
+    float* vec = offsets + 2 * DIM;
+    const int raw_elems = chunk * (4 * DIM + p.cols);
+    const int raw_bytes = (raw_elems * static_cast<int>(sizeof(scalar_t)) + 15) / 16 * 16;
+    float* o_part = vec + chunk * 5 * DIM;  // [chunk][threads]
+    unsigned char* raw_base = reinterpret_cast<unsigned char*>(o_part + chunk * blockDim.x);
+    __shared__ float inv_norm[kMaxChunk];
+
+    const int e = blockIdx.x, head = blockIdx.y;
+    const int col0 = blockIdx.z * p.cols;
+    const int n_cols = min(p.cols, DIM - col0);
+    const int tid = threadIdx.x;
+    const int col = tid / PARTS, part = tid % PARTS;
+    const bool active = col < n_cols;
+    const int first = p.first_rows[e], count = p.counts[e];
+    const int64_t hoff = static_cast<int64_t>(head) * DIM;
+    float* mine = p.state + (static_cast<int64_t>(p.slots[e]) * p.n_heads + head) * DIM * DIM;
+
+    load_chunk<scalar_t>(p, reinterpret_cast<scalar_t*>(raw_base), first, min(chunk, count), hoff, col0, n_cols);
+    for (int i = tid; i < DIM; i += blockDim.x) {
+        offsets[i] = p.w0[hoff + i];
+        offsets[DIM + i] = p.a0[hoff + i];
+    }
+    float S[ROWS];
+#pragma unroll
+    for (int m = 0; m < ROWS; ++m) {
+        S[m] = active ? mine[static_cast<int64_t>(part * ROWS + m) * DIM + col0 + col] : 0.0f;
+    }
+
+    int buffer = 0;
+    for (int done = 0; done < count; done += chunk, buffer ^= 1) {
+        const int n = min(chunk, count - done);
+        const scalar_t* raw = reinterpret_cast<const scalar_t*>(raw_base + buffer * raw_bytes);
+        if (done + chunk < count) {
+            load_chunk<scalar_t>(p, reinterpret_cast<scalar_t*>(raw_base + (buffer ^ 1) * raw_bytes),
+                                 first + done + chunk, min(chunk, count - done - chunk), hoff, col0, n_cols);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();
+        prepare_chunk<scalar_t>(p, raw, vec, offsets, inv_norm, n, DIM);
+        const scalar_t* raw_v = raw + chunk * 4 * DIM;
+        // A lane's share of the five vectors of a token, fetched one token ahead of its use.
+        float nk[ROWS], nu[ROWS], nw[ROWS], na[ROWS], nr[ROWS];
+        auto fetch = [&](int c) {
+            const float* token = vec + c * 5 * DIM + part * ROWS;
+#pragma unroll
+            for (int q = 0; q < ROWS / 4; ++q) {
+                *reinterpret_cast<float4*>(nk + 4 * q) = *reinterpret_cast<const float4*>(token + 4 * q);
+                *reinterpret_cast<float4*>(nu + 4 * q) = *reinterpret_cast<const float4*>(token + DIM + 4 * q);
+                *reinterpret_cast<float4*>(nw + 4 * q) = *reinterpret_cast<const float4*>(token + 2 * DIM + 4 * q);
+                *reinterpret_cast<float4*>(na + 4 * q) = *reinterpret_cast<const float4*>(token + 3 * DIM + 4 * q);
+                *reinterpret_cast<float4*>(nr + 4 * q) = *reinterpret_cast<const float4*>(token + 4 * DIM + 4 * q);
+            }
+        };
+        fetch(0);
+        float nv = active ? pl_load(raw_v + col) : 0.0f;
+        for (int c = 0; c < n; ++c) {
+            float sk[ROWS], su[ROWS], sw[ROWS], sau[ROWS], sr[ROWS];
+#pragma unroll
+            for (int m = 0; m < ROWS; ++m) {
+                sk[m] = nk[m];
+                su[m] = nu[m];
+                sw[m] = nw[m];
+                sau[m] = na[m];
+                sr[m] = nr[m];
+            }
+            const float vj = nv;
+            if (c + 1 < n) {
+                fetch(c + 1);
+                nv = active ? pl_load(raw_v + (c + 1) * p.cols + col) : 0.0f;
+            }
+            float dot = 0.0f, dot_odd = 0.0f;
+#pragma unroll
+            for (int m = 0; m < ROWS; m += 2) {
+                dot = fmaf(su[m], S[m], dot);
+                dot_odd = fmaf(su[m + 1], S[m + 1], dot_odd);
+            }
+            dot += dot_odd;
+#pragma unroll
+            for (int offset = PARTS >> 1; offset > 0; offset >>= 1) {
+                dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+            }
+            float o = 0.0f, o_odd = 0.0f;
+#pragma unroll
+            for (int m = 0; m < ROWS; m += 2) {
+                S[m] = fmaf(sk[m], vj, fmaf(-sau[m], dot, sw[m] * S[m]));
+                o = fmaf(S[m], sr[m], o);
+                S[m + 1] = fmaf(sk[m + 1], vj, fmaf(-sau[m + 1], dot, sw[m + 1] * S[m + 1]));
+                o_odd = fmaf(S[m + 1], sr[m + 1], o_odd);
+            }
+            // The lanes' shares of o wait in shared memory; they are added up after the chunk,
+            // off the path from one token to the next.
+            o_part[c * blockDim.x + tid] = o + o_odd;
+        }
+        __syncwarp();  // (a column's lanes sit in one warp)
+        for (int c = part; c < n; c += PARTS) {
+            const float* shares = o_part + c * blockDim.x + col * PARTS;
+            float o = shares[0];
+#pragma unroll
+            for (int q = 1; q < PARTS; ++q) {
+                o += shares[q];
+            }
+            if (active) {
+                p.o_raw[static_cast<int64_t>(first + done + c) * p.n_heads * DIM + hoff + col0 + col] = o;
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int m = 0; m < ROWS; ++m) {
+        if (active) {
+            mine[static_cast<int64_t>(part * ROWS + m) * DIM + col0 + col] = S[m];
+        }
+    }
+}
+
+template <typename scalar_t, int DIM, int PARTS>
+void launch_scan_static(const ScanParams& p, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(delta_rule_scan_static_kernel<scalar_t, DIM, PARTS>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    }
+    pl_launch_overlapped(delta_rule_scan_static_kernel<scalar_t, DIM, PARTS>, grid, dim3(threads), smem, stream, p);
+}
+
+template <typename scalar_t>
+void launch_scan(const ScanParams& p, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
+    if (p.dim == 128 && p.parts == 16) {
+        launch_scan_static<scalar_t, 128, 16>(p, grid, threads, smem, stream);
+    } else if (p.dim == 64 && p.parts == 8) {
+        launch_scan_static<scalar_t, 64, 8>(p, grid, threads, smem, stream);
+    } else if (p.dim == 32 && p.parts == 4) {
+        launch_scan_static<scalar_t, 32, 4>(p, grid, threads, smem, stream);
+    } else if (p.dim == 16 && p.parts == 2) {
+        launch_scan_static<scalar_t, 16, 2>(p, grid, threads, smem, stream);
+    } else {
+        if (smem > 48 * 1024) {
+            cudaFuncSetAttribute(delta_rule_scan_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+        }
+        pl_launch_overlapped(delta_rule_scan_kernel<scalar_t>, grid, dim3(threads), smem, stream, p);
     }
 }
 
@@ -288,6 +461,11 @@ PL_API int pl_delta_rule(const void* r, const void* k, const void* v, const void
     // Columns per CTA: all of the head's where a CTA holds them (the CTAs of one head repeat the
     // work between chunks), else as many as it holds.
     int cols = kMaxThreads / parts > dim ? dim : kMaxThreads / parts;
+    // Half of that where a head then still fills a warp per scheduler: two CTAs per head on two SMs
+    // issue a token's instructions in half the time, and what they both do between chunks is small.
+    if (cols == dim && cols * parts > 256 && cols % 2 == 0) {
+        cols /= 2;
+    }
     const int width = dtype == PL_F32 ? 4 : 2;
     if ((cols * width) % 16 != 0 && cols < dim) {
         int wider = (cols * width + 15) / 16 * 16 / width;  // (blocks of columns that start on 16 bytes)
@@ -309,15 +487,13 @@ PL_API int pl_delta_rule(const void* r, const void* k, const void* v, const void
     p.async_loads = (dim * width) % 16 == 0 && (cols * width) % 16 == 0 && (row_stride * width) % 16 == 0 &&
         (w_row_stride * width) % 16 == 0 && aligned(r) && aligned(k) && aligned(v) && aligned(a_pre) && aligned(w_pre);
     const int raw_bytes = (p.chunk * (4 * dim + cols) * width + 15) / 16 * 16;
-    const size_t smem = static_cast<size_t>(2 * dim + p.chunk * 5 * dim) * sizeof(float) + 2 * raw_bytes;
     int threads = (cols * parts + 31) / 32 * 32;
+    // (offsets, a chunk's vectors, the lanes' shares of o, two buffers of raw projections)
+    const size_t smem = static_cast<size_t>(2 * dim + p.chunk * 5 * dim + p.chunk * threads) * sizeof(float) +
+        2 * raw_bytes;
     const dim3 grid(n_entries, n_heads, col_blocks);
     PL_DISPATCH_DTYPE(dtype, "delta_rule", {
-        if (smem > 48 * 1024) {
-            cudaFuncSetAttribute(delta_rule_scan_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem));
-        }
-        pl_launch_overlapped(delta_rule_scan_kernel<scalar_t>, grid, dim3(threads), smem, stream, p);
+        launch_scan<scalar_t>(p, grid, threads, smem, stream);
         PL_CHECK_LAUNCH("delta_rule");
         const int64_t pairs = static_cast<int64_t>(n_tokens) * n_heads;
         pl_launch_overlapped(delta_rule_finish_kernel<scalar_t>, dim3(static_cast<unsigned>((pairs + 3) / 4)), dim3(128),
