@@ -419,6 +419,35 @@ __global__ void bias_act_kernel(const scalar_t* in, int64_t in_row_stride, const
     }
 }
 
+// Four elements per thread (widths that are multiples of 4, rows that start on 16 bytes).
+template <typename scalar_t>
+__global__ void bias_act_vec_kernel(const scalar_t* in, int64_t in_row_stride, const scalar_t* __restrict__ bias,
+                                    scalar_t* out, int64_t tokens, int width, int act) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    const int per_row = width / 4;
+    const int64_t total = tokens * per_row;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t t = i / per_row;
+        const int c = 4 * static_cast<int>(i - t * per_row);
+        float4 z = pl_load4(in + t * in_row_stride + c);
+        if (bias != nullptr) {
+            const float4 b = pl_load4(bias + c);
+            z.x += b.x; z.y += b.y; z.z += b.z; z.w += b.w;
+        }
+        if (act == 1) {
+            z.x = z.x > 0.0f ? z.x * z.x : 0.0f;
+            z.y = z.y > 0.0f ? z.y * z.y : 0.0f;
+            z.z = z.z > 0.0f ? z.z * z.z : 0.0f;
+            z.w = z.w > 0.0f ? z.w * z.w : 0.0f;
+        } else if (act == 2) {
+            z = make_float4(tanhf(z.x), tanhf(z.y), tanhf(z.z), tanhf(z.w));
+        }
+        pl_store4(out + t * width + c, z);
+    }
+}
+
 }  // namespace
 
 PL_API int pl_bias_act(const void* in, int64_t in_row_stride, const void* bias, void* out, int n_tokens, int width,
@@ -430,6 +459,17 @@ PL_API int pl_bias_act(const void* in, int64_t in_row_stride, const void* bias, 
     }
     const int threads = 256;
     const int64_t total = static_cast<int64_t>(n_tokens) * width;
+    if (width % 4 == 0 && in_row_stride % 4 == 0 &&
+        ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        const int blocks = static_cast<int>(std::min<int64_t>((total / 4 + threads - 1) / threads, 148 * 16));
+        PL_DISPATCH_DTYPE(dtype, "bias_act", {
+            pl_launch_overlapped(bias_act_vec_kernel<scalar_t>, blocks, threads, 0, stream,
+                                 static_cast<const scalar_t*>(in), in_row_stride, static_cast<const scalar_t*>(bias),
+                                 static_cast<scalar_t*>(out), static_cast<int64_t>(n_tokens), width, act);
+        });
+        PL_CHECK_LAUNCH("bias_act");
+        return 0;
+    }
     const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
     PL_DISPATCH_DTYPE(dtype, "bias_act", {
         pl_launch_overlapped(bias_act_kernel<scalar_t>, blocks, threads, 0, stream, static_cast<const scalar_t*>(in),

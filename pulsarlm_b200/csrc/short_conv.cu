@@ -75,6 +75,85 @@ __global__ void short_conv_kernel(const scalar_t* __restrict__ h, const float* _
     }
 }
 
+// The same for the usual few taps and widths that are multiples of 4: a block walks kRowsPerBlock
+// rows of 4 * 128 channels with the earlier inputs in registers, so a row of h is read once
+// instead of `taps` times and the weights once a block. Same products in the same order as the
+// kernel above: same bits.
+constexpr int kRowsPerBlock = 16;
+
+template <typename scalar_t, int TAPS>
+__global__ void __launch_bounds__(128) short_conv_rows_kernel(
+        const scalar_t* __restrict__ h, const float* __restrict__ weight, const scalar_t* __restrict__ state,
+        const int32_t* __restrict__ entry, const int32_t* __restrict__ slots, scalar_t* __restrict__ out, int n_tokens,
+        int width) {
+    pl_grid_trigger();
+    constexpr int REACH = TAPS - 1;
+    const int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
+    const int t0 = blockIdx.x * kRowsPerBlock;
+    if (c >= width) {
+        return;
+    }
+    float w[4][TAPS];  // (weights: read before the wait on earlier kernels)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+            w[q][j] = weight[static_cast<int64_t>(c + q) * TAPS + j];
+        }
+    }
+    pl_grid_wait();
+    float4 window[REACH > 0 ? REACH : 1];  // the inputs before the row at hand, oldest first
+    float4 last = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    int last_entry = -1;
+    for (int t = t0; t < min(t0 + kRowsPerBlock, n_tokens); ++t) {
+        const int e = entry[t];
+        if (t == t0) {
+            int inside = 0;
+            while (inside < REACH && t - inside - 1 >= 0 && entry[t - inside - 1] == e) {
+                ++inside;
+            }
+            const scalar_t* old = state + static_cast<int64_t>(slots[e]) * REACH * width;
+#pragma unroll
+            for (int j = 0; j < REACH; ++j) {
+                const int back = REACH - j;
+                window[j] = back <= inside ? pl_load4(h + static_cast<int64_t>(t - back) * width + c)
+                                           : pl_load4(old + static_cast<int64_t>(REACH - (back - inside)) * width + c);
+            }
+        } else if (e != last_entry) {
+            const scalar_t* old = state + static_cast<int64_t>(slots[e]) * REACH * width;
+#pragma unroll
+            for (int j = 0; j < REACH; ++j) {
+                window[j] = pl_load4(old + static_cast<int64_t>(j) * width + c);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j + 1 < REACH; ++j) {
+                window[j] = window[j + 1];
+            }
+            if (REACH > 0) {
+                window[REACH - 1] = last;
+            }
+        }
+        const float4 own = pl_load4(h + static_cast<int64_t>(t) * width + c);
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < REACH; ++j) {
+            acc.x = fmaf(w[0][j], window[j].x, acc.x);
+            acc.y = fmaf(w[1][j], window[j].y, acc.y);
+            acc.z = fmaf(w[2][j], window[j].z, acc.z);
+            acc.w = fmaf(w[3][j], window[j].w, acc.w);
+        }
+        acc.x = fmaf(w[0][REACH], own.x, acc.x);
+        acc.y = fmaf(w[1][REACH], own.y, acc.y);
+        acc.z = fmaf(w[2][REACH], own.z, acc.z);
+        acc.w = fmaf(w[3][REACH], own.w, acc.w);
+        pl_store4(out + static_cast<int64_t>(t) * width + c,
+                  make_float4(own.x + acc.x, own.y + acc.y, own.z + acc.z, own.w + acc.w));
+        last = own;
+        last_entry = e;
+    }
+}
+
 // The state after the step: the last taps - 1 inputs of each sequence. A portion of at least
 // taps - 1 rows writes them from its last rows; a shorter one is handled by its first row's
 // block, which also moves the older rows up.
@@ -135,6 +214,37 @@ PL_API int pl_short_conv(const void* h, const float* weight, const void* state, 
     }
     const int vectors = width % 4 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(state) |
                                             reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    if (vectors && taps >= 2 && taps <= 6) {
+        const dim3 grid((n_tokens + kRowsPerBlock - 1) / kRowsPerBlock, (width / 4 + 127) / 128);
+#define PL_CONV_ROWS(T)                                                                                          \
+    pl_launch_overlapped(short_conv_rows_kernel<scalar_t, T>, grid, dim3(128), 0, stream,                        \
+                         static_cast<const scalar_t*>(h), weight, static_cast<const scalar_t*>(state), entry,    \
+                         slots, static_cast<scalar_t*>(out), n_tokens, width)
+        if (dtype == PL_F32) {
+            using scalar_t = float;
+            switch (taps) {
+                case 2: PL_CONV_ROWS(2); break;
+                case 3: PL_CONV_ROWS(3); break;
+                case 4: PL_CONV_ROWS(4); break;
+                case 5: PL_CONV_ROWS(5); break;
+                default: PL_CONV_ROWS(6); break;
+            }
+        } else if (dtype == PL_BF16) {
+            using scalar_t = __nv_bfloat16;
+            switch (taps) {
+                case 2: PL_CONV_ROWS(2); break;
+                case 3: PL_CONV_ROWS(3); break;
+                case 4: PL_CONV_ROWS(4); break;
+                case 5: PL_CONV_ROWS(5); break;
+                default: PL_CONV_ROWS(6); break;
+            }
+        } else {
+            return pl_fail(2, "short_conv: unknown dtype code %d", dtype);
+        }
+#undef PL_CONV_ROWS
+        PL_CHECK_LAUNCH("short_conv");
+        return 0;
+    }
     const int lanes = vectors ? width / 4 : width;
     const int threads = lanes >= 256 ? 256 : ((lanes + 31) / 32) * 32;
     PL_DISPATCH_DTYPE(dtype, "short_conv", {

@@ -29,16 +29,19 @@ def _i32(values):
 
 # --------------------------------------------------------------------------- mechanisms alone
 
-@pytest.mark.parametrize("taps", [1, 2, 4, 5])
+@pytest.mark.parametrize("taps", [1, 2, 4, 5, 8])
+@pytest.mark.parametrize("width", [24, 23, 520])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_short_convolution_kernels(taps, dtype):
+def test_short_convolution_kernels(taps, width, dtype):
     """Entries of 1 to 9 rows (shorter and longer than the taps), fed in two steps, with
-    histories that are zero (a sequence's first tokens) and not; outputs and states."""
+    histories that are zero (a sequence's first tokens) and not; outputs and states. (Widths
+    that are multiples of 4 with few taps take the kernel that walks rows, others the plain one;
+    520 channels span two blocks of it.)"""
     ops = _ops()
-    width, slots = 24, 7
+    slots = 7
     gen = torch.Generator().manual_seed(taps)
     weight = torch.randn((width, taps), generator=gen)
-    lengths = [[1, 2, 3, 5, 9], [3, 1, 1, 2, 4]]
+    lengths = [[1, 2, 3, 5, 9], [3, 1, 1, 2, 40]]
     state = torch.zeros((slots, taps - 1, width), dtype=dtype, device=DEV)
     history = {e: None for e in range(5)}
     slot_of = [4, 0, 6, 2, 1]
@@ -57,7 +60,7 @@ def test_short_convolution_kernels(taps, dtype):
         for e, n in enumerate(step):
             want, history[e] = plain.short_convolution(rows[e].double(), weight.double(), history[e])
             got = out[at: at + n].cpu().double()
-            assert (got - want).abs().max() < (1e-5 if dtype == torch.float32 else 4e-2)
+            assert rt.relative_error(got, want) < (1e-5 if dtype == torch.float32 else 1e-2)
             if taps > 1:
                 assert torch.equal(state[slot_of[e]].cpu().double(), history[e])
             at += n
@@ -471,6 +474,56 @@ def test_sizes_come_from_the_configuration():
         steps = [([("p", tokens["p"][:20], list(range(20)))], [])]
         steps += [([("p", [t], [0])], []) for t in tokens["p"][20:]]
         tm.check(tokens, harness.replay(tm.runner(8), steps), "sizes of one")
+
+
+def _random_config(seed: int) -> dict:
+    """Sizes, constants and layer order drawn at random: widths that are no multiple of 8, odd
+    head counts, head sizes and ranks with and without a kernel of their own, windows from 1 up,
+    layers with and without feed-forward or window."""
+    gen = torch.Generator().manual_seed(seed)
+
+    def pick(options):
+        return options[int(torch.randint(0, len(options), (1,), generator=gen))]
+
+    width = pick([36, 52, 64, 100, 136])
+    layers = []
+    for _ in range(pick([2, 3, 4, 5])):
+        ff = pick([None, 40, 72, 130])
+        if pick([0, 1, 1]) == 0:
+            layers.append(rt.delta_layer(pick([1, 2, 3, 5]), pick([8, 12, 16, 24, 32, 40, 64]), ff))
+        else:
+            layers.append(rt.latent_layer(pick([1, 2, 3, 4, 7]), pick([8, 12, 16, 20, 32]), pick([8, 12, 16, 24, 40]),
+                                          pick([8, 24, 32, 40, 48, 64, 80, 96, 112, 128, 136]),
+                                          pick([None, 1, 2, 5, 16, 17, 31, 33, 50]), pick([0.2, 0.35, 1.0]), ff))
+    cfg = {"architecture": "Rerilorn", "vocab": pick([64, 101, 257]), "width": width,
+           "norm": {"eps": pick([1e-6, 1e-5, 1e-3])}, "residual_mult": pick([0.25, 0.5, 1.0, 1.5]),
+           "embedding": {"scale": pick([1.0, 2.5, width ** 0.5])}, "layers": layers}
+    taps = pick([0, 1, 2, 3, 4, 6])
+    if taps:
+        cfg["canon"] = {"taps": taps}
+    return cfg
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_configurations_drawn_at_random(seed):
+    """Each drawn model under a mixed schedule (portions, single tokens, a request that ends and
+    one that takes its slot), float32 against the plain implementation at the float32 bar, then
+    bfloat16 at its own (some of these models amplify a rounding at a few positions: see
+    TinyRerilorn.check)."""
+    cfg = _random_config(seed)
+    page = [16, 32, 64][seed % 3]
+    for dtype in ("float32", "bfloat16"):
+        tm = rt.TinyRerilorn("-", dtype, seed=seed, cfg=cfg)
+        tokens = {r: rt.random_tokens(cfg, n, 100 + seed + i) for i, (r, n) in enumerate({"a": 70, "b": 23, "c": 41}.items())}
+        a, b, c = tokens["a"], tokens["b"], tokens["c"]
+        steps = [([("a", a[:35], list(range(35))), ("b", b[:2], [0, 1])], []),
+                 ([("a", a[35:36], [0]), ("b", b[2:23], list(range(21)))], ["b"]),
+                 ([("a", a[36:37], [0]), ("c", c[:3], [0, 1, 2])], []),
+                 ([("c", c[3:40], list(range(37))), ("a", a[37:38], [0])], [])]
+        steps += [([("a", [a[i]], [0])] + ([("c", [c[40]], [0])] if i == 38 else []), ["c"] if i == 38 else [])
+                  for i in range(38, 70)]
+        runner = tm.runner(-(-70 // page) + -(-41 // page) + 2, slots=2, page=page)
+        tm.check(tokens, harness.replay(runner, steps), f"random configuration {seed}", touchy=True)
 
 
 def test_missing_and_misshapen_tensors_are_named():
