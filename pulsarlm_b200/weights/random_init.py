@@ -65,6 +65,9 @@ def random_tensors(
     for name, need in needs.items():
         if need.optional:
             continue
+        if any(extent < 0 for extent in need.shape):
+            raise ValueError(f"random weights: the size of {name!r} {list(need.shape)} is one that only a checkpoint "
+                             f"gives; name it in the configuration (a delta-rule mixer's `decay_rank`)")
         t = torch.empty(need.shape, dtype=dtype, device=device)
         if need.role == "vector":
             fill_random(t, seed, name, vector_std, 1.0)

@@ -587,3 +587,60 @@ def test_engine_in_bfloat16_stays_close():
         ref = tm.plain_logits(full[:-1])
         for i, row in enumerate(request.logits):
             assert rt.relative_error(row, ref[len(prompt) - 1 + i]) < rt.TOLERANCE["bfloat16"]
+
+
+def test_command_line_random_model_generate_and_replay(tmp_path, capsys):
+    """`models list`, `models random`, `generate` and `replay` of the command line for this
+    architecture: greedy tokens equal the plain implementation's on the written weights, and
+    the replayed logits too."""
+    import json
+
+    import numpy as np
+    from safetensors.torch import load_file
+
+    from pulsarlm_b200 import cli
+
+    assert cli.main(["models", "list"]) == 0
+    assert "Rerilorn" in capsys.readouterr().out.split()
+    cfg = json.loads(json.dumps(rt.CONFIGS["B"][0]))
+    with pytest.raises(ValueError, match="decay_rank"):
+        cli.main(["models", "random", str(tmp_path / "none"), "--config", _write(tmp_path / "c0.json", cfg)])
+    for layer in cfg["layers"]:
+        if layer["type"] == "general_delta":
+            layer["mixer"]["decay_rank"] = 5
+    folder = str(tmp_path / "model")
+    assert cli.main(["models", "random", folder, "--config", _write(tmp_path / "c1.json", cfg), "--seed", "3",
+                     "--dtype", "float32", "--std", "0.3"]) == 0
+    capsys.readouterr()
+    weights = {k: v.double() for k, v in load_file(folder + "/model.safetensors").items()}
+    prompt = rt.random_tokens(cfg, 19, 90)
+    assert cli.main(["generate", folder, "--dtype", "float32", "--prompt_ids", ",".join(map(str, prompt)),
+                     "--max_tokens", "8", "--ignore_eos"]) == 0
+    record = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    tokens = list(prompt)
+    for _ in range(8):
+        tokens.append(int(plain.forward(cfg, weights, tokens)[0][-1].argmax()))
+    assert record["output_ids"] == tokens[len(prompt):]
+    # the trace replay of the command line over the same folder
+    import io
+
+    from pulsarlm_b200.engine import trace
+
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:11], "want": [3, 10]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": tokens[11:12], "want": [0]}], "end": ["a"]}]
+    out = io.StringIO()
+    assert trace.run(["--model", folder, "--dtype", "float32", "--out", str(tmp_path / "out"), "--max-tokens", "64"],
+                     stdin=io.StringIO("\n".join(json.dumps(s) for s in steps) + "\n"), stdout=out) == 0
+    assert out.getvalue().split() == ["done", "0", "done", "1"]
+    ref = plain.forward(cfg, weights, tokens[:12])[0]
+    got0 = torch.from_numpy(np.fromfile(str(tmp_path / "out" / "0.f32"), dtype="<f4").reshape(2, -1))
+    got1 = torch.from_numpy(np.fromfile(str(tmp_path / "out" / "1.f32"), dtype="<f4").reshape(1, -1))
+    assert rt.relative_error(got0, ref[[3, 10]]) < 2e-4 and rt.relative_error(got1, ref[[11]]) < 2e-4
+
+
+def _write(path, text) -> str:
+    import json
+
+    with open(path, "w") as f:
+        json.dump(text, f)
+    return str(path)
