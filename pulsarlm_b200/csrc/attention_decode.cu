@@ -154,6 +154,9 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
     const int my_tiles = t1 > t0 + warp ? (t1 - t0 - warp + WARPS - 1) / WARPS : 0;
 
     int my_page = 0;  // lane L holds the page of this warp's tile 32 * (i / 32) + L
+    // One pool for keys and values (a cached latent that serves as both, never with a new key to
+    // rotate and store): a tile is fetched once and read as K and as V.
+    const bool shared_rows = p.v_pool == p.k_pool && p.k_new == nullptr;
     auto issue = [&](int i) {  // loads this warp's i-th tile into stage i % STAGES
         if (i % 32 == 0 && i < my_tiles) {
             // one coalesced look-up of the block table for the next 32 tiles
@@ -180,7 +183,9 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
                 const int r = c / kChunks, ch = c % kChunks;
                 const int dst = r * kRowSmem + ((ch ^ (r & 7)) * 16);
                 cp_async_16(stage + dst, ksrc + r * kRowBytes + ch * 16);
-                cp_async_16(stage + kTileBytes + dst, vsrc + r * kRowBytes + ch * 16);
+                if (!shared_rows) {
+                    cp_async_16(stage + kTileBytes + dst, vsrc + r * kRowBytes + ch * 16);
+                }
             }
         }
         cp_async_commit();
@@ -383,7 +388,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
         {
             const int mi = lane >> 3, r = lane & 7;
             const int key = (mi & 1) * 8 + r;
-            const unsigned char* vt = stage + kTileBytes;
+            const unsigned char* vt = shared_rows ? stage : stage + kTileBytes;
 #pragma unroll
             for (int dp = 0; dp < HD / 16; ++dp) {
                 uint32_t b[4];

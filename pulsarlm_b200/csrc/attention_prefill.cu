@@ -81,6 +81,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
     }
     cp_async_commit();
 
+    // One pool for keys and values (a cached latent that serves as both): the tile is fetched once
+    // and read as K and as V.
+    const bool shared_rows = p.v_pool == p.k_pool;
     auto issue = [&](int j, int stage) {
         unsigned char* k_s = kv_s + stage * 2 * kTileBytes;
         unsigned char* v_s = k_s + kTileBytes;
@@ -103,7 +106,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
             }
             const int dst = swizzled(r, ch, kRowBytes);
             cp_async_16_or_zero(k_s + dst, p.k_pool + offset, valid);
-            cp_async_16_or_zero(v_s + dst, p.v_pool + offset, valid);
+            if (!shared_rows) {
+                cp_async_16_or_zero(v_s + dst, p.v_pool + offset, valid);
+            }
         }
         cp_async_commit();
     };
@@ -143,7 +148,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
         }
         __syncthreads();
         const unsigned char* k_s = kv_s + stage * 2 * kTileBytes;
-        const unsigned char* v_s = k_s + kTileBytes;
+        const unsigned char* v_s = shared_rows ? k_s : k_s + kTileBytes;
         const int key0 = j * kBN;
         // A warp whose rows all come before this tile (causal) or after it (window) has nothing to add.
         const bool warp_active = key0 <= warp_last &&
