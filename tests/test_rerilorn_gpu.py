@@ -572,6 +572,34 @@ def test_greedy_generation_through_the_engine(cuda_graphs):
         assert engine.runner.graph_steps > 0
 
 
+def test_engine_preempts_and_recomputes_with_states():
+    """So few pages that running requests are preempted (pages and state slot given back, the
+    request recomputed from its start later): the tokens are still the plain implementation's,
+    so no state of an earlier life leaks into the recomputation."""
+    from pulsarlm_b200.engine.engine import Engine
+
+    cfg = json_copy(rt.CONFIGS["B"][0])  # (its first latent layer has no window: every page is kept)
+    tm = rt.TinyRerilorn("-", "float32", seed=4, cfg=cfg)
+    engine = Engine(tm.folder, dtype="float32", device=DEV, page_size=16, n_pages=7, max_requests=4,
+                    prefill_tokens_per_step=16)
+    prompts = [rt.random_tokens(cfg, n, 95 + i) for i, n in enumerate([30, 25, 20])]
+    requests = [engine.submit(p, max_tokens=20, ignore_eos=True) for p in prompts]
+    for _ in range(600):
+        if not engine.has_work():
+            break
+        engine.step()
+    assert not engine.has_work() and engine.scheduler.preemptions > 0
+    for prompt, request in zip(prompts, requests):
+        assert request.finish_reason == "length"
+        assert list(request.output) == _plain_greedy(tm, prompt, 20)
+
+
+def json_copy(value):
+    import json
+
+    return json.loads(json.dumps(value))
+
+
 def test_engine_in_bfloat16_stays_close():
     from pulsarlm_b200.engine.engine import Engine
 
