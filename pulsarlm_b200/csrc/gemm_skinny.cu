@@ -55,9 +55,14 @@ struct SkinnyParams {
     // output): the epilogue warps, idle until the accumulator is done, read g and u, form
     // the product in fp32, round it once and store it where the MMA reads its B operand
     // (same layout as a TMA tile with 128-byte swizzle). T <= 16.
+    // 2: x = act(z + bias) made on the way in the same way, z [T, K] a projection's output (rows
+    // ld_gated apart), bias [K] or nullptr, act 1: relu(.)^2, 2: tanh(.) (fp32, one rounding: the
+    // bits of the bias-and-activation kernel).
     int x_mode;
     const __nv_bfloat16* gated;
     int64_t ld_gated;
+    const __nv_bfloat16* in_bias;
+    int in_act;
 };
 
 // The receive buffer: [rank][feature of mine][token], rows of tn + 4 floats (16-byte
@@ -228,7 +233,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16);
         pl_grid_wait();
         if constexpr (TN == 16) {
-            if (p.x_mode == 1) {
+            if (p.x_mode != 0) {
                 // These four warps make the activation tiles, each every fourth stage, so that one
                 // warp's waits, fence and arrival overlap the others' arithmetic: lane (token, half
                 // a row) of a 16 x 64 tile, four 16-byte chunks each. A warp asks for its next
@@ -244,7 +249,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         const int k = (kb0 + u) * kBlockK + (chunk0 + c) * 8;
                         if (row_ok && u < n_units && k < p.k) {  // (k is a multiple of 8, and so is p.k)
                             g[c] = *reinterpret_cast<const uint4*>(g_row + k);
-                            v[c] = *reinterpret_cast<const uint4*>(g_row + p.k + k);
+                            if (p.x_mode == 1) {
+                                v[c] = *reinterpret_cast<const uint4*>(g_row + p.k + k);
+                            } else {
+                                v[c] = p.in_bias != nullptr ? *reinterpret_cast<const uint4*>(p.in_bias + k)
+                                                            : make_uint4(0u, 0u, 0u, 0u);
+                            }
                         } else {
                             g[c] = make_uint4(0u, 0u, 0u, 0u);
                             v[c] = g[c];
@@ -266,9 +276,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const float2 g = __bfloat1622float2(g2[j]), v = __bfloat1622float2(u2[j]);
-                            // (the SwiGLU kernel's own expression: the same bits)
-                            const __nv_bfloat162 pair = __floats2bfloat162_rn(
-                                __fdividef(g.x, 1.0f + __expf(-g.x)) * v.x, __fdividef(g.y, 1.0f + __expf(-g.y)) * v.y);
+                            __nv_bfloat162 pair;
+                            if (p.x_mode == 1) {
+                                // (the SwiGLU kernel's own expression: the same bits)
+                                pair = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-g.x)) * v.x,
+                                                             __fdividef(g.y, 1.0f + __expf(-g.y)) * v.y);
+                            } else {
+                                float z0 = g.x + v.x, z1 = g.y + v.y;
+                                if (p.in_act == 1) {
+                                    z0 = z0 > 0.0f ? z0 * z0 : 0.0f;
+                                    z1 = z1 > 0.0f ? z1 * z1 : 0.0f;
+                                } else if (p.in_act == 2) {
+                                    z0 = tanhf(z0);
+                                    z1 = tanhf(z1);
+                                }
+                                pair = __floats2bfloat162_rn(z0, z1);
+                            }
                             o[j] = *reinterpret_cast<const uint32_t*>(&pair);
                         }
                         *reinterpret_cast<uint4*>(tile + (((chunk0 + c) ^ (token & 7)) << 4)) = out;
@@ -535,7 +558,8 @@ PL_API int pl_gemm_bf16_skinny_max_tokens() { return 64; }
 namespace {
 
 int run_skinny(const void* x, const void* w, void* y, int t, int n, int k, int64_t ldx, int64_t ldw, int64_t ldy,
-               int out_f32, int x_mode, int32_t* status, cudaStream_t stream) {
+               int out_f32, int x_mode, int32_t* status, cudaStream_t stream, const void* in_bias = nullptr,
+               int in_act = 0) {
     const int tn = t <= 16 ? 16 : (t <= 32 ? 32 : 64);
     if (const int code = tn == 16 ? configure<16>() : (tn == 32 ? configure<32>() : configure<64>())) {
         return code;
@@ -564,6 +588,8 @@ int run_skinny(const void* x, const void* w, void* y, int t, int n, int k, int64
     p.x_mode = x_mode;
     p.gated = static_cast<const __nv_bfloat16*>(x);
     p.ld_gated = ldx;
+    p.in_bias = static_cast<const __nv_bfloat16*>(in_bias);
+    p.in_act = in_act;
     switch (plan.tn) {
         case 16: return launch_skinny<16>(map_w, map_x, p, plan, stream);
         case 32: return launch_skinny<32>(map_w, map_x, p, plan, stream);
@@ -603,4 +629,22 @@ PL_API int pl_gemm_bf16_skinny_gated_in(const void* gated, const void* w, void* 
                "gemm_bf16_skinny_gated_in: operands must be 16-byte aligned");
     PL_REQUIRE(ldy >= n, "gemm_bf16_skinny_gated_in: ldy=%lld is smaller than n=%d", static_cast<long long>(ldy), n);
     return run_skinny(gated, w, y, t, n, k, ld_gated, ldw, ldy, out_f32, 1, status, stream);
+}
+
+// y[T, N] = act(z + bias)[T, K] w[N, K]^T for z [T, K] bf16 (a projection's output, rows ldz
+// apart), bias bf16 [K] or nullptr, act 1: relu(.)^2, 2: tanh(.): the activation is formed as
+// the product reads z (fp32, one rounding, as pl_bias_act does) and is never written. T <= 16.
+PL_API int pl_gemm_bf16_skinny_act_in(const void* z, const void* bias, const void* w, void* y, int t, int n, int k,
+                                      int64_t ldz, int64_t ldw, int64_t ldy, int act, int out_f32, int32_t* status,
+                                      cudaStream_t stream) {
+    PL_REQUIRE(t >= 1 && t <= 16 && n >= 1 && k >= 8 && k % 8 == 0 && ldz % 8 == 0 && ldw % 8 == 0 && ldz >= k &&
+                   (act == 1 || act == 2),
+               "gemm_bf16_skinny_act_in: unsupported sizes t=%d n=%d k=%d ld=%lld ldw=%lld act=%d (t <= 16; k and the "
+               "leading dimensions must be multiples of 8)",
+               t, n, k, static_cast<long long>(ldz), static_cast<long long>(ldw), act);
+    PL_REQUIRE((reinterpret_cast<uintptr_t>(z) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(bias) & 15) == 0,
+               "gemm_bf16_skinny_act_in: operands must be 16-byte aligned");
+    PL_REQUIRE(ldy >= n, "gemm_bf16_skinny_act_in: ldy=%lld is smaller than n=%d", static_cast<long long>(ldy), n);
+    return run_skinny(z, w, y, t, n, k, ldz, ldw, ldy, out_f32, 2, status, stream, bias, act);
 }

@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 22
+ABI_VERSION = 23
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -65,6 +65,7 @@ _SIGNATURES = {
     "pl_attention_decode_ctas_per_sm": [_I32],
     "pl_layer_forward": [_PTR, _PTR, _PTR],
     "pl_gemm_bf16_skinny_gated_in": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR],
+    "pl_gemm_bf16_skinny_act_in": [_PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _I32, _PTR, _PTR],
     "pl_fill_random": [_PTR, _I64, _I32, ctypes.c_uint64, ctypes.c_uint64, _F32, _F32, _PTR],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
     "pl_attention_prefill": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32, _PTR, _I64,
@@ -450,6 +451,24 @@ def gemm_bf16_gated_in(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor
     _call("pl_gemm_bf16_skinny_gated_in", _p(gate_up), _p(w), _p(out), t, n, k,
           gate_up.stride(0) if t > 1 else two_k, w.stride(0) if n > 1 else k, out.stride(0) if t > 1 else n,
           int(out.dtype == torch.float32), _p(status), _stream())
+
+
+def gemm_bf16_act_in(z: torch.Tensor, bias: torch.Tensor | None, w: torch.Tensor, out: torch.Tensor, act: str,
+                     status: torch.Tensor | None = None) -> None:
+    """out[T, N] = act(z + bias) @ w[N, K]^T for z [T, K] (a projection's output, row stride free), act
+    "relu2" or "tanh": the skinny kernel forms the activation as it reads z (fp32, one rounding, the
+    bits of bias_act) and never writes it. T <= 16."""
+    _dev(z, bias, w, out, status)
+    assert z.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+    t, k = z.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and out.shape == (t, n) and t <= GEMM_GATED_IN_MAX_TOKENS and act in ("relu2", "tanh")
+    assert z.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.shape == (k,) and bias.is_contiguous()
+    _call("pl_gemm_bf16_skinny_act_in", _p(z), _p(bias), _p(w), _p(out), t, n, k, z.stride(0) if t > 1 else k,
+          w.stride(0) if n > 1 else k, out.stride(0) if t > 1 else n, BIAS_ACT[act], int(out.dtype == torch.float32),
+          _p(status), _stream())
 
 
 def rope_kv_write(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | None, pos: torch.Tensor,

@@ -12,7 +12,7 @@ import math
 import torch
 
 from ..kernels import ops
-from .linear import gated_feed_forward, linear
+from .linear import activated_linear, gated_feed_forward, linear
 from .registry import BuildContext, Part, register_part
 from .spec import PartSpec, TensorNeed
 
@@ -272,9 +272,7 @@ class PlainMLP(Part):
 
     def forward(self, h: torch.Tensor, batch, bias_taken: bool = False) -> torch.Tensor:
         """bias_taken: the caller adds `down_bias` itself (inside the kernel that reads the output)."""
-        z = linear(h, self.up)
-        ops.bias_act(z, self.up_bias, z, self.activation)
-        y = linear(z, self.down)
+        y = activated_linear(linear(h, self.up), self.up_bias, self.activation, self.down)
         if self.down_bias is not None and not bias_taken:
             ops.bias_act(y, self.down_bias, y, "none")
         return y

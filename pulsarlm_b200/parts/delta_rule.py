@@ -8,7 +8,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from .linear import linear
+from .linear import activated_linear, linear
 from .registry import BuildContext, Part, register_part
 from .spec import PartSpec, StateNeed, TensorNeed
 
@@ -107,9 +107,7 @@ class GeneralDelta(Part):
         width = self.n_heads * self.head_dim
         proj = linear(h, self.stacked)                              # [T, 5 * width + inner]
         r, k, v, g, a = (proj[:, i * width:(i + 1) * width] for i in range(5))
-        inner = torch.empty((tokens, self.inner), dtype=h.dtype, device=h.device)
-        ops.bias_act(proj[:, 5 * width:], None, inner, "tanh")      # the decay's inner activation
-        w_pre = linear(inner, self.w2)
+        w_pre = activated_linear(proj[:, 5 * width:], None, "tanh", self.w2)   # the decay's inner activation
         plan = batch.plans[SEQUENCE_ROWS_KEY]
         out = torch.empty((tokens, width), dtype=h.dtype, device=h.device)
         ops.delta_rule(r, k, v, g, a, w_pre, self.w0, self.a0, self.norm, self.binding.states, plan["first"],

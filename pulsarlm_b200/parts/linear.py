@@ -135,3 +135,24 @@ def gated_feed_forward(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tenso
         ops.gemm_bf16_gated_in(linear(x, gate_up), down, out)
         return out
     return linear(gated_linear(x, gate_up), down)
+
+
+ACT_IN = os.environ.get("PULSARLM_B200_ACT_IN", "1") != "0"  # (0: always the bias-and-activation kernel)
+
+
+def activated_linear(z: torch.Tensor, bias: torch.Tensor | None, act: str, weight: torch.Tensor) -> torch.Tensor:
+    """act(z + bias) W^T -> [T, N] for z [T, K] (a projection's output; its rows may be columns of a
+    wider matrix), act "relu2" or "tanh". For a handful of tokens in bfloat16 the skinny kernel forms
+    the activation itself as it reads z (one launch fewer, the activation never written; the same
+    bits); else the bias-and-activation kernel followed by `linear`."""
+    tokens, k = z.shape
+    if (ACT_IN and z.dtype == torch.bfloat16 == weight.dtype and tokens <= ops.GEMM_GATED_IN_MAX_TOKENS
+            and z.stride(1) == 1 and weight.stride(1) == 1 and z.data_ptr() % 16 == 0
+            and own_kernel_for(tokens, weight.shape[0], z.device, k) == "skinny"
+            and ops.gemm_bf16_supports(tokens, weight.shape[0], k, z.stride(0) if tokens > 1 else k, weight.stride(0))):
+        out = torch.empty((tokens, weight.shape[0]), dtype=z.dtype, device=z.device)
+        ops.gemm_bf16_act_in(z, bias, weight, out, act)
+        return out
+    activated = torch.empty((tokens, k), dtype=z.dtype, device=z.device)
+    ops.bias_act(z, bias, activated, act)
+    return linear(activated, weight)

@@ -152,6 +152,31 @@ def test_convolution_riding_along_in_the_norm_kernel(taps, dtype):
         assert torch.equal(fused, apart) and torch.equal(x1, x2) and torch.equal(states[0], states[1])
 
 
+@pytest.mark.parametrize("act", ["relu2", "tanh"])
+@pytest.mark.parametrize("tokens,k,n", [(1, 16, 384), (5, 64, 200), (16, 392, 72), (8, 2048, 1024)])
+def test_activation_formed_inside_the_product(act, tokens, k, n):
+    """The skinny product that forms act(z + bias) as it reads z, against the activation kernel
+    followed by the same product: equal bits (z a slice of a wider matrix, with and without bias)."""
+    from pulsarlm_b200.parts import linear as lin
+
+    ops = _ops()
+    gen = torch.Generator().manual_seed(k)
+    wide = torch.randn((tokens, k + 24), generator=gen).to(torch.bfloat16).to(DEV)
+    z = wide[:, 8: 8 + k]
+    weight = (torch.randn((n, k), generator=gen) / k ** 0.5).to(torch.bfloat16).to(DEV)
+    for bias in (None, torch.randn(k, generator=gen).to(torch.bfloat16).to(DEV)):
+        activated = torch.empty((tokens, k), dtype=torch.bfloat16, device=DEV)
+        ops.bias_act(z, bias, activated, act)
+        want = torch.empty((tokens, n), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_bf16(activated, weight, want, kernel="skinny")
+        got = torch.empty_like(want)
+        ops.gemm_bf16_act_in(z, bias, weight, got, act)
+        assert torch.equal(got, want)
+        exact = activated.double() @ weight.double().t()
+        assert rt.relative_error(got.cpu(), exact.cpu()) < 1e-2
+        assert torch.equal(lin.activated_linear(z, bias, act, weight), want)
+
+
 def _latent_case(ops, n_heads, rank, page, window, lengths, queries, dtype, seed, spike=None):
     """Latents of requests of `lengths` tokens in pages handed out in a scrambled order;
     `queries`: (request, position) pairs. spike = (distance, height): the latent `distance`
