@@ -18,6 +18,20 @@
 
 namespace {
 
+// Four elements of the engine's dtype as one load or store.
+template <typename scalar_t>
+struct FourOf;
+template <>
+struct FourOf<float> {
+    using type = float4;
+};
+template <>
+struct FourOf<__nv_bfloat16> {
+    using type = bf16x4;
+};
+template <typename scalar_t>
+using float4_or_half = typename FourOf<scalar_t>::type;
+
 template <typename scalar_t>
 __global__ void add_normed_rmsnorm_kernel(float* __restrict__ x, const scalar_t* __restrict__ y,
                                           const scalar_t* __restrict__ bias, const float* __restrict__ wy,
@@ -132,6 +146,120 @@ __global__ void add_normed_rmsnorm_kernel(float* __restrict__ x, const scalar_t*
     }
 }
 
+// The same with the row in registers (widths that are multiples of 4 up to 4 * VECS * the block
+// size, rows that start on 16 bytes): one pass over memory, the weights read before the wait on
+// earlier kernels. A thread holds the same elements and adds its squares in the same order as the
+// wide form above, so both give the same bits.
+template <typename scalar_t, int VECS>
+__global__ void __launch_bounds__(512) add_normed_rmsnorm_reg_kernel(
+        float* __restrict__ x, const scalar_t* __restrict__ y, const scalar_t* __restrict__ bias,
+        const float* __restrict__ wy, float mult, float eps_y, const float* __restrict__ w, float eps,
+        scalar_t* __restrict__ out, const int32_t* __restrict__ rows, int hidden, const float* __restrict__ conv_weight,
+        scalar_t* __restrict__ conv_state, const int32_t* __restrict__ slots, int taps) {
+    pl_grid_trigger();
+    __shared__ float scratch[32];
+    const int n_vec = hidden / 4;
+    float4 gy[VECS], gw[VECS];
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        gy[i] = c < n_vec ? pl_load4(wy + 4 * c) : zero;
+        gw[i] = c < n_vec && w != nullptr ? pl_load4(w + 4 * c) : zero;
+    }
+    pl_grid_wait();
+    const int r = blockIdx.x;
+    const int64_t s = rows != nullptr ? rows[r] : r;
+    float* xr = x + s * hidden;
+    const scalar_t* yr = y + s * hidden;
+    float4 v[VECS], xv[VECS];
+    float local = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n_vec) {
+            xv[i] = pl_load4(xr + 4 * c);
+            float4 u = pl_load4(yr + 4 * c);
+            if (bias != nullptr) {
+                const float4 b = pl_load4(bias + 4 * c);
+                u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+            }
+            v[i] = u;
+            local += u.x * u.x;
+            local += u.y * u.y;
+            local += u.z * u.z;
+            local += u.w * u.w;
+        }
+    }
+    const float inv_y = 1.0f / sqrtf(pl_block_sum(local, scratch) / static_cast<float>(hidden) + eps_y);
+    local = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n_vec) {
+            const float4 u = v[i];
+            v[i] = make_float4(xv[i].x + mult * (u.x * inv_y * gy[i].x), xv[i].y + mult * (u.y * inv_y * gy[i].y),
+                               xv[i].z + mult * (u.z * inv_y * gy[i].z), xv[i].w + mult * (u.w * inv_y * gy[i].w));
+            if (rows == nullptr) {
+                pl_store4(xr + 4 * c, v[i]);
+            }
+            local += v[i].x * v[i].x;
+            local += v[i].y * v[i].y;
+            local += v[i].z * v[i].z;
+            local += v[i].w * v[i].w;
+        }
+    }
+    if (out == nullptr) {
+        return;
+    }
+    const float inv = 1.0f / sqrtf(pl_block_sum(local, scratch) / static_cast<float>(hidden) + eps);
+    scalar_t* outr = out + static_cast<int64_t>(r) * hidden;
+    const int reach = taps - 1;
+    scalar_t* mine = conv_weight != nullptr ? conv_state + static_cast<int64_t>(slots[r]) * reach * hidden : nullptr;
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c >= n_vec) {
+            continue;
+        }
+        const float4 h4 = make_float4(v[i].x * inv * gw[i].x, v[i].y * inv * gw[i].y, v[i].z * inv * gw[i].z,
+                                      v[i].w * inv * gw[i].w);
+        if (conv_weight == nullptr) {
+            pl_store4(outr + 4 * c, h4);
+            continue;
+        }
+        // The convolution of a step of single tokens (see the plain form): four channels at a time.
+        alignas(16) scalar_t rounded[4];
+        pl_store4(rounded, h4);
+        const float4 own = pl_load4(rounded);
+        const float* cw = conv_weight + static_cast<int64_t>(4 * c) * taps;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int j = 0; j < reach; ++j) {
+            alignas(16) scalar_t old_raw[4];
+            *reinterpret_cast<float4_or_half<scalar_t>*>(old_raw) =
+                *reinterpret_cast<const float4_or_half<scalar_t>*>(mine + static_cast<int64_t>(j) * hidden + 4 * c);
+            const float4 old = pl_load4(old_raw);
+            acc.x = fmaf(cw[j], old.x, acc.x);
+            acc.y = fmaf(cw[taps + j], old.y, acc.y);
+            acc.z = fmaf(cw[2 * taps + j], old.z, acc.z);
+            acc.w = fmaf(cw[3 * taps + j], old.w, acc.w);
+            if (j > 0) {
+                *reinterpret_cast<float4_or_half<scalar_t>*>(mine + static_cast<int64_t>(j - 1) * hidden + 4 * c) =
+                    *reinterpret_cast<const float4_or_half<scalar_t>*>(old_raw);
+            }
+        }
+        acc.x = fmaf(cw[reach], own.x, acc.x);
+        acc.y = fmaf(cw[taps + reach], own.y, acc.y);
+        acc.z = fmaf(cw[2 * taps + reach], own.z, acc.z);
+        acc.w = fmaf(cw[3 * taps + reach], own.w, acc.w);
+        if (reach > 0) {
+            *reinterpret_cast<float4_or_half<scalar_t>*>(mine + static_cast<int64_t>(reach - 1) * hidden + 4 * c) =
+                *reinterpret_cast<const float4_or_half<scalar_t>*>(rounded);
+        }
+        pl_store4(outr + 4 * c, make_float4(own.x + acc.x, own.y + acc.y, own.z + acc.z, own.w + acc.w));
+    }
+}
+
 }  // namespace
 
 // x fp32 [T, hidden]; y [T, hidden] and the optional bias [hidden] in the engine's dtype;
@@ -162,6 +290,30 @@ PL_API int pl_add_normed_rmsnorm(float* x, const void* y, const void* bias, cons
     int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
     threads = threads < 64 ? 64 : threads > 512 ? 512 : threads;
     const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+    const bool conv_rows_aligned = conv_weight == nullptr || taps == 1 || (reinterpret_cast<uintptr_t>(conv_state) & 15) == 0;
+    if (vectors && hidden <= 4 * 4 * threads && conv_rows_aligned) {
+        const int vecs = (hidden / 4 + threads - 1) / threads;
+#define PL_NORM_REG(V)                                                                                              \
+    err = pl_launch_overlapped(add_normed_rmsnorm_reg_kernel<scalar_t, V>, dim3(n_rows), dim3(threads), 0, stream,  \
+                               x, static_cast<const scalar_t*>(y), static_cast<const scalar_t*>(bias), wy, mult,     \
+                               eps_y, w, eps, static_cast<scalar_t*>(out), rows, hidden, conv_weight,                \
+                               static_cast<scalar_t*>(conv_state), slots, taps)
+        cudaError_t err = cudaSuccess;
+        if (dtype == PL_F32) {
+            using scalar_t = float;
+            if (vecs == 1) { PL_NORM_REG(1); } else if (vecs == 2) { PL_NORM_REG(2); } else { PL_NORM_REG(4); }
+        } else if (dtype == PL_BF16) {
+            using scalar_t = __nv_bfloat16;
+            if (vecs == 1) { PL_NORM_REG(1); } else if (vecs == 2) { PL_NORM_REG(2); } else { PL_NORM_REG(4); }
+        } else {
+            return pl_fail(2, "add_normed_rmsnorm: unknown dtype code %d", dtype);
+        }
+#undef PL_NORM_REG
+        if (err != cudaSuccess) {
+            return pl_fail(3, "add_normed_rmsnorm: launch failed: %s", cudaGetErrorString(err));
+        }
+        return 0;
+    }
     PL_DISPATCH_DTYPE(dtype, "add_normed_rmsnorm", {
         if (smem > 48 * 1024) {
             cudaFuncSetAttribute(add_normed_rmsnorm_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
