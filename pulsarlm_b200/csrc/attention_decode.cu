@@ -108,7 +108,9 @@ __host__ __device__ constexpr int merge_bytes(int n_vec, int splits) {
 
 // One share of one (token, kv head): split `split` of `n_splits` equal shares, or in
 // work-list mode the tiles [item_first, item_first + item_tiles).
-template <int HD, int WARPS, int STAGES>
+// EXTRAS: the build that takes sinks, gates, split weights and one pool for keys and values (see
+// PlAttentionExtras); the plain build is compiled without any of it.
+template <int HD, int WARPS, int STAGES, bool EXTRAS>
 __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, unsigned char* smem, const int split,
                                                        const int kv_head, const int t, const int n_splits,
                                                        const int item_first, const int item_tiles) {
@@ -156,7 +158,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
     int my_page = 0;  // lane L holds the page of this warp's tile 32 * (i / 32) + L
     // One pool for keys and values (a cached latent that serves as both, never with a new key to
     // rotate and store): a tile is fetched once and read as K and as V.
-    const bool shared_rows = p.v_pool == p.k_pool && p.k_new == nullptr;
+    const bool shared_rows = EXTRAS && p.v_pool == p.k_pool && p.k_new == nullptr;
     auto issue = [&](int i) {  // loads this warp's i-th tile into stage i % STAGES
         if (i % 32 == 0 && i < my_tiles) {
             // one coalesced look-up of the block table for the next 32 tiles
@@ -370,7 +372,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
             pa[1] = pack_bf16(p02, p03);
             pa[2] = pack_bf16(p10, p11);
             pa[3] = pack_bf16(p12, p13);
-            if (p.split_weights) {
+            if (EXTRAS && p.split_weights) {
                 // what the rounding to bfloat16 lost, as a second bfloat16 term
                 pb[0] = pack_bf16(p00 - bf16_round(p00), p01 - bf16_round(p01));
                 pb[1] = pack_bf16(p02 - bf16_round(p02), p03 - bf16_round(p03));
@@ -396,7 +398,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
                 ldmatrix_x4_trans(b, vt + key * kRowSmem + ((chunk ^ (key & 7)) * 16));
                 mma_bf16(o[2 * dp], pa, b[0], b[1]);
                 mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
-                if (p.split_weights) {
+                if (EXTRAS && p.split_weights) {
                     mma_bf16(o[2 * dp], pb, b[0], b[1]);
                     mma_bf16(o[2 * dp + 1], pb, b[2], b[3]);
                 }
@@ -509,7 +511,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
             }
             const int h = kv_head * p.group + r;
             __nv_bfloat16* dst = p.out + t * p.out_row_stride + static_cast<int64_t>(h) * HD + d;
-            if (p.sinks != nullptr || p.gate != nullptr) {
+            if (EXTRAS && (p.sinks != nullptr || p.gate != nullptr)) {
                 const float f = pl_attention_row_factor(m, l, p.sinks, p.gate, p.gate_row_stride, t, h);
                 dst[0] = __float2bfloat16_rn(acc.x * f);
                 dst[1] = __float2bfloat16_rn(acc.y * f);
@@ -545,7 +547,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
         const int h = kv_head * p.group + r;
         if (n_splits == 1) {
             p.out[t * p.out_row_stride + static_cast<int64_t>(h) * HD + d] = __float2bfloat16_rn(
-                p.sinks != nullptr || p.gate != nullptr
+                EXTRAS && (p.sinks != nullptr || p.gate != nullptr)
                     ? acc * pl_attention_row_factor(m, l, p.sinks, p.gate, p.gate_row_stride, t, h)
                     : (l > 0.0f ? acc / l : 0.0f));
         } else {
@@ -687,7 +689,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
 // head) pairs off a queue, in list order, each as soon as it is free: counters[0] is the
 // queue's head and counters[1] counts the CTAs that found it empty; the last of them puts
 // both back to zero for the next launch.
-template <int HD, int WARPS, int STAGES>
+template <int HD, int WARPS, int STAGES, bool EXTRAS = false>
 __global__ void __launch_bounds__(WARPS * 32, HD <= 64 ? 4 : 2) attention_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     pl_grid_trigger();  // positions and block tables are step inputs, read before the wait
@@ -718,7 +720,7 @@ __global__ void __launch_bounds__(WARPS * 32, HD <= 64 ? 4 : 2) attention_decode
             first = item.y;
             tiles = item.z;
         }
-        attention_decode_share<HD, WARPS, STAGES>(p, smem, split, kv_head, t, n_splits, first, tiles);
+        attention_decode_share<HD, WARPS, STAGES, EXTRAS>(p, smem, split, kv_head, t, n_splits, first, tiles);
         if (!queued) {
             return;
         }
@@ -795,20 +797,20 @@ constexpr int ring_bytes(int head_dim) { return kWarps * stages_of(head_dim) * 2
 
 constexpr int kClusterSplitsMax = 16;  // the largest cluster the part takes (above 8: opted into per kernel)
 
-template <int HD>
+template <int HD, bool EXTRAS>
 int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool allow_cluster, cudaStream_t stream) {
     constexpr int rings = ring_bytes(HD);
     static_assert(rings >= kWarps * 16 * (HD + 2) * 4, "the merge buffers must fit in the rings");
     constexpr int most_merge = merge_bytes(16 * (HD / 4), kClusterSplitsMax) + 1024;
     static bool configured = false, big_clusters = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, stages_of(HD)>,
+        cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, stages_of(HD), EXTRAS>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, rings + most_merge);
         if (err != cudaSuccess) {
             return pl_fail(3, "attention_decode: cannot set shared memory size: %s", cudaGetErrorString(err));
         }
         // clusters of more than eight CTAs (if the device refuses, such split counts go through scratch)
-        big_clusters = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, stages_of(HD)>,
+        big_clusters = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, stages_of(HD), EXTRAS>,
                                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         cudaGetLastError();
         configured = true;
@@ -835,7 +837,7 @@ int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool
             int device = 0, sms = 0, each = 0;
             cudaGetDevice(&device);
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&each, attention_decode_kernel<HD, kWarps, stages_of(HD)>,
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&each, attention_decode_kernel<HD, kWarps, stages_of(HD), EXTRAS>,
                                                               kWarps * 32, rings) != cudaSuccess || each < 1) {
                 cudaGetLastError();
                 each = 1;
@@ -851,7 +853,7 @@ int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool
         int64_t ctas = static_cast<int64_t>(n_tokens) * n_kv_heads;
         ctas = ctas < resident ? resident : ctas;
         ctas = ctas > n_work ? n_work : ctas;
-        pl_launch_overlapped(attention_decode_kernel<HD, kWarps, stages_of(HD)>, dim3(static_cast<int>(ctas), 1, 1),
+        pl_launch_overlapped(attention_decode_kernel<HD, kWarps, stages_of(HD), EXTRAS>, dim3(static_cast<int>(ctas), 1, 1),
                              kWarps * 32, rings, stream, p);
         PL_CHECK_LAUNCH("attention_decode (work list)");
         return 0;
@@ -871,13 +873,13 @@ int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool
         attributes[1].val.programmaticStreamSerializationAllowed = 1;
         config.attrs = attributes;
         config.numAttrs = pl_overlap_enabled() ? 2 : 1;
-        const cudaError_t err = cudaLaunchKernelEx(&config, attention_decode_kernel<HD, kWarps, stages_of(HD)>, p);
+        const cudaError_t err = cudaLaunchKernelEx(&config, attention_decode_kernel<HD, kWarps, stages_of(HD), EXTRAS>, p);
         if (err != cudaSuccess) {
             return pl_fail(3, "attention_decode: launch failed: %s", cudaGetErrorString(err));
         }
         return 0;
     }
-    pl_launch_overlapped(attention_decode_kernel<HD, kWarps, stages_of(HD)>, grid, kWarps * 32, rings, stream, p);
+    pl_launch_overlapped(attention_decode_kernel<HD, kWarps, stages_of(HD), EXTRAS>, grid, kWarps * 32, rings, stream, p);
     PL_CHECK_LAUNCH("attention_decode");
     if (p.n_splits > 1) {
         pl_launch_overlapped(attention_decode_merge_kernel<HD>, dim3(p.n_heads, n_tokens), HD <= 64 ? 64 : 128, 0,
@@ -1048,7 +1050,9 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
     PL_REQUIRE(tile_max == nullptr || max_tiles >= static_cast<int64_t>(table_width) * page_size / kTile,
                "attention_decode: %d tiles per row of tile maxima do not cover a table of %d pages", max_tiles,
                table_width);
-#define PL_CALL(HD) launch_decode<HD>(p, n_tokens, n_kv_heads, allow_cluster, stream)
+#define PL_CALL(HD)                                                                       \
+    (extras != nullptr ? launch_decode<HD, true>(p, n_tokens, n_kv_heads, allow_cluster, stream) \
+                       : launch_decode<HD, false>(p, n_tokens, n_kv_heads, allow_cluster, stream))
     PL_DECODE_HEAD_SIZES(head_dim, PL_CALL, pl_fail(2, "attention_decode: head size %d", head_dim))
 #undef PL_CALL
 }

@@ -49,7 +49,9 @@ struct PrefillParams {
     int split_weights;
 };
 
-template <int HD>
+// EXTRAS: the build that takes sinks, gates, split weights and one pool for keys and values; the
+// plain build is compiled without any of it.
+template <int HD, bool EXTRAS>
 __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const PrefillParams p) {
     // Rows in shared memory are as long as the next multiple of 64 elements, so that the swizzle
     // (which permutes a row's first eight or sixteen chunks) stays inside the row at any head size.
@@ -83,7 +85,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
 
     // One pool for keys and values (a cached latent that serves as both): the tile is fetched once
     // and read as K and as V.
-    const bool shared_rows = p.v_pool == p.k_pool;
+    const bool shared_rows = EXTRAS && p.v_pool == p.k_pool;
     auto issue = [&](int j, int stage) {
         unsigned char* k_s = kv_s + stage * 2 * kTileBytes;
         unsigned char* v_s = k_s + kTileBytes;
@@ -238,7 +240,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
                     pa[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
                     pa[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
                     pa[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
-                    if (p.split_weights) {
+                    if (EXTRAS && p.split_weights) {
                         // what the rounding to bfloat16 lost, as a second bfloat16 term
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
                         ldmatrix_x4_trans(b, v_s + swizzled(key, 2 * dp + (mi >> 1), kRowBytes));
                         mma_bf16(o[2 * dp], pa, b[0], b[1]);
                         mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
-                        if (p.split_weights) {
+                        if (EXTRAS && p.split_weights) {
                             mma_bf16(o[2 * dp], pb, b[0], b[1]);
                             mma_bf16(o[2 * dp + 1], pb, b[2], b[3]);
                         }
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
     const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
     float inv_lo = l_lo > 0.0f ? 1.0f / l_lo : 0.0f, inv_hi = l_hi > 0.0f ? 1.0f / l_hi : 0.0f;
-    if (p.sinks != nullptr || p.gate != nullptr) {
+    if (EXTRAS && (p.sinks != nullptr || p.gate != nullptr)) {
         inv_lo = pl_attention_row_factor(m_lo, l_lo, p.sinks, p.gate, p.gate_row_stride, row0 + min(r_lo, n_rows - 1),
                                          head);
         inv_hi = pl_attention_row_factor(m_hi, l_hi, p.sinks, p.gate, p.gate_row_stride, row0 + min(r_hi, n_rows - 1),
@@ -291,21 +293,28 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
     }
 }
 
-template <int HD>
-int launch_prefill(const PrefillParams& p, int n_tiles, int n_heads, cudaStream_t stream) {
+template <int HD, bool EXTRAS>
+int launch_prefill_build(const PrefillParams& p, int n_tiles, int n_heads, cudaStream_t stream) {
     constexpr int smem = kBM * padded_row_bytes(HD) + 2 * 2 * kBN * padded_row_bytes(HD);
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attention_prefill_kernel<HD>,
+        cudaError_t err = cudaFuncSetAttribute(attention_prefill_kernel<HD, EXTRAS>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (err != cudaSuccess) {
             return pl_fail(3, "attention_prefill: cannot set shared memory size: %s", cudaGetErrorString(err));
         }
         configured = true;
     }
-    attention_prefill_kernel<HD><<<dim3(n_heads, n_tiles), kThreads, smem, stream>>>(p);
+    attention_prefill_kernel<HD, EXTRAS><<<dim3(n_heads, n_tiles), kThreads, smem, stream>>>(p);
     PL_CHECK_LAUNCH("attention_prefill");
     return 0;
+}
+
+template <int HD>
+int launch_prefill(const PrefillParams& p, int n_tiles, int n_heads, cudaStream_t stream) {
+    const bool extras = p.sinks != nullptr || p.gate != nullptr || p.split_weights || p.v_pool == p.k_pool;
+    return extras ? launch_prefill_build<HD, true>(p, n_tiles, n_heads, stream)
+                  : launch_prefill_build<HD, false>(p, n_tiles, n_heads, stream);
 }
 
 }  // namespace

@@ -31,6 +31,8 @@
 // pulsarlm-core/src/engine/model/llama.cpp:67-69, 81, 91, 93).
 #include "tcgen05_helpers.cuh"
 
+#include <type_traits>
+
 namespace {
 
 constexpr int kTileM = 128;
@@ -90,7 +92,9 @@ constexpr int stages_within(int tn, int budget) {
 
 // (Two CTAs of a launch with a CTA for every SM and more share an SM: the registers must
 // allow it, 168 a thread at most.)
-template <int TN>
+// ACT_IN: the build whose activations are act(z + bias) made on the way in (x_mode 2); the plain
+// build (x from TMA, or the gated activation) is compiled without it.
+template <int TN, bool ACT_IN = false>
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const SkinnyParams p) {
@@ -238,6 +242,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 // warp's waits, fence and arrival overlap the others' arithmetic: lane (token, half
                 // a row) of a 16 x 64 tile, four 16-byte chunks each. A warp asks for its next
                 // stage's g and u before it works on the one it has.
+                // (the two modes are compiled apart: neither pays for the other's branches)
+                auto produce = [&](auto mode) {
+                constexpr int MODE = decltype(mode)::value;
                 const int mine = warp - 2;                     // stages mine, mine + 4, ...
                 const int token = lane >> 1, chunk0 = (lane & 1) * 4;
                 const bool row_ok = token < p.t;
@@ -249,7 +256,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         const int k = (kb0 + u) * kBlockK + (chunk0 + c) * 8;
                         if (row_ok && u < n_units && k < p.k) {  // (k is a multiple of 8, and so is p.k)
                             g[c] = *reinterpret_cast<const uint4*>(g_row + k);
-                            if (p.x_mode == 1) {
+                            if constexpr (MODE == 1) {
                                 v[c] = *reinterpret_cast<const uint4*>(g_row + p.k + k);
                             } else {
                                 v[c] = p.in_bias != nullptr ? *reinterpret_cast<const uint4*>(p.in_bias + k)
@@ -277,7 +284,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         for (int j = 0; j < 4; ++j) {
                             const float2 g = __bfloat1622float2(g2[j]), v = __bfloat1622float2(u2[j]);
                             __nv_bfloat162 pair;
-                            if (p.x_mode == 1) {
+                            if constexpr (MODE == 1) {
                                 // (the SwiGLU kernel's own expression: the same bits)
                                 pair = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-g.x)) * v.x,
                                                              __fdividef(g.y, 1.0f + __expf(-g.y)) * v.y);
@@ -316,6 +323,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     if (!make(u + 4, g_in[1], u_in[1])) {
                         break;
                     }
+                }
+                };
+                if constexpr (ACT_IN) {
+                    produce(std::integral_constant<int, 2>{});
+                } else {
+                    produce(std::integral_constant<int, 1>{});
                 }
             }
         }
@@ -426,6 +439,10 @@ int configure() {
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(gemm_skinny_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                smem_for(TN, stages_within(TN, kSmemLarge)));
+        if (err == cudaSuccess && TN == 16) {
+            err = cudaFuncSetAttribute(gemm_skinny_kernel<TN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       smem_for(TN, stages_within(TN, kSmemLarge)));
+        }
         if (err != cudaSuccess) {
             return pl_fail(3, "gemm_skinny: cannot configure the kernel: %s", cudaGetErrorString(err));
         }
@@ -533,7 +550,8 @@ int launch_skinny(const CUtensorMap& map_w, const CUtensorMap& map_x, const Skin
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = pl_overlap_enabled() ? 2 : 1;
-    const cudaError_t err = cudaLaunchKernelEx(&config, gemm_skinny_kernel<TN>, map_w, map_x, p);
+    const cudaError_t err = p.x_mode == 2 ? cudaLaunchKernelEx(&config, gemm_skinny_kernel<TN, true>, map_w, map_x, p)
+                                          : cudaLaunchKernelEx(&config, gemm_skinny_kernel<TN>, map_w, map_x, p);
     if (err != cudaSuccess) {
         return pl_fail(3, "gemm_skinny: launch failed: %s", cudaGetErrorString(err));
     }
