@@ -1,0 +1,247 @@
+// The gated delta rule with a decay per key channel: a recurrent mixer whose state per head
+// is a matrix S [dim, vdim] (key channel x value channel) kept in fp32 from token to token.
+//
+//   q^ = q / sqrt(|q|^2 + unit_eps) * q_scale,  k^ = k / sqrt(|k|^2 + unit_eps)      per q/k head
+//   g  = exp(-exp(A_h) * softplus(a~ + dt_bias))                                      per head and key channel
+//   b  = sigmoid(b~)                                                                  per head
+//   S <- diag(g) S;  u = b * (v - S^T k^);  S <- S + k^ u^T;  o = S^T q^               (o reads the new S)
+//   out = o * rsqrt(mean(o^2) + eps) * norm * sigmoid(gate~)                          per head over vdim
+//
+// q, k, v arrive filtered and activated (the engine's dtype), a~, b~ and gate~ as projected;
+// everything above is fp32. Head h reads q/k head h / (heads / qk_heads).
+//
+// The scan: a CTA per (batch entry, head, block of value columns) walks the entry's rows in
+// order. A column of S never meets another column, so each column lives in registers:
+// `parts` neighbouring lanes share a column and each holds every parts-th of its rows. The
+// rows are taken in chunks: all threads turn a chunk's projections into the fp32 vectors
+// q^, k^, g and the scalar b in shared memory (the unit factors by a warp per token, the
+// exponentials one (token, channel) per thread), then the tokens update the state one after
+// the other with nothing but the shuffles among a column's lanes between them. The raw o
+// goes to scratch in fp32; a second kernel norms it per head, applies the norm's weight and
+// the gate and rounds once. The order of every sum depends on the sizes alone, so a token's
+// result depends on the tokens before it only: not on how the prompt was cut, on the chunks
+// or on the rest of the batch.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kRows = 16;      // rows of a column one lane holds at most
+constexpr int kChunkMost = 16;
+
+struct GatedDeltaParams {
+    const void* q;
+    const void* k;
+    const void* v;
+    int64_t qkv_stride;
+    const void* b_pre;
+    int64_t b_stride;
+    const void* a_pre;
+    int64_t a_stride;
+    const float* a_log;
+    const float* dt_bias;
+    float* state;
+    const int32_t* first_rows;
+    const int32_t* counts;
+    const int32_t* slots;
+    float* o_raw;
+    int n_heads, qk_heads, dim, vdim, parts, cols, chunk;
+    float unit_eps, q_scale;
+};
+
+__device__ __forceinline__ float softplus_f32(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+template <typename scalar_t>
+__global__ void __launch_bounds__(512) gated_delta_scan_kernel(const GatedDeltaParams p) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    extern __shared__ float shared[];
+    const int dim = p.dim, parts = p.parts, chunk = p.chunk, cols = p.cols;
+    float* sq = shared;                 // [chunk][dim]
+    float* sk = sq + chunk * dim;       // [chunk][dim]
+    float* sg = sk + chunk * dim;       // [chunk][dim]
+    float* sv = sg + chunk * dim;       // [chunk][cols]
+    float* sb = sv + chunk * cols;      // [chunk]
+    float* inv_q = sb + chunk;          // [chunk]
+    float* inv_k = inv_q + chunk;       // [chunk]
+
+    const int e = blockIdx.x, head = blockIdx.y;
+    const int qk_head = head / (p.n_heads / p.qk_heads);
+    const int col0 = blockIdx.z * cols;
+    const int n_cols = min(cols, p.vdim - col0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+    const int col = tid / parts, part = tid % parts;
+    const bool active = col < n_cols;
+    const int first = p.first_rows[e], count = p.counts[e];
+    const scalar_t* q = static_cast<const scalar_t*>(p.q) + static_cast<int64_t>(qk_head) * dim;
+    const scalar_t* k = static_cast<const scalar_t*>(p.k) + static_cast<int64_t>(qk_head) * dim;
+    const scalar_t* v = static_cast<const scalar_t*>(p.v) + static_cast<int64_t>(head) * p.vdim + col0;
+    const scalar_t* a_pre = static_cast<const scalar_t*>(p.a_pre) + static_cast<int64_t>(head) * dim;
+    const scalar_t* b_pre = static_cast<const scalar_t*>(p.b_pre) + head;
+    const float rate = expf(p.a_log[head]);
+    const float* bias = p.dt_bias + static_cast<int64_t>(head) * dim;
+    float* mine = p.state + ((static_cast<int64_t>(p.slots[e]) * p.n_heads + head) * dim) * p.vdim + col0;
+
+    float S[kRows];
+#pragma unroll
+    for (int m = 0; m < kRows; ++m) {
+        const int i = part + m * parts;
+        S[m] = active && i < dim ? mine[static_cast<int64_t>(i) * p.vdim + col] : 0.0f;
+    }
+
+    for (int done = 0; done < count; done += chunk) {
+        const int n = min(chunk, count - done);
+        const int64_t t0 = first + done;
+        __syncthreads();  // (the chunk before has been read)
+        for (int c = warp; c < n; c += warps) {
+            const scalar_t* qr = q + (t0 + c) * p.qkv_stride;
+            const scalar_t* kr = k + (t0 + c) * p.qkv_stride;
+            float qq = 0.0f, kk = 0.0f;
+            for (int i = lane; i < dim; i += 32) {
+                const float a = pl_load(qr + i), b = pl_load(kr + i);
+                qq = fmaf(a, a, qq);
+                kk = fmaf(b, b, kk);
+            }
+            qq = pl_warp_sum(qq);
+            kk = pl_warp_sum(kk);
+            if (lane == 0) {
+                inv_q[c] = p.q_scale / sqrtf(qq + p.unit_eps);
+                inv_k[c] = 1.0f / sqrtf(kk + p.unit_eps);
+                sb[c] = 1.0f / (1.0f + expf(-pl_load(b_pre + (t0 + c) * p.b_stride)));
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < n * dim; idx += blockDim.x) {
+            const int c = idx / dim, i = idx - c * dim;
+            sq[idx] = pl_load(q + (t0 + c) * p.qkv_stride + i) * inv_q[c];
+            sk[idx] = pl_load(k + (t0 + c) * p.qkv_stride + i) * inv_k[c];
+            sg[idx] = expf(-rate * softplus_f32(pl_load(a_pre + (t0 + c) * p.a_stride + i) + bias[i]));
+        }
+        for (int idx = tid; idx < n * cols; idx += blockDim.x) {
+            const int c = idx / cols, j = idx - c * cols;
+            sv[idx] = j < n_cols ? pl_load(v + (t0 + c) * p.qkv_stride + j) : 0.0f;
+        }
+        __syncthreads();
+        for (int c = 0; c < n; ++c) {
+            const float* kq = sq + c * dim;
+            const float* kk = sk + c * dim;
+            const float* kg = sg + c * dim;
+            float dot = 0.0f;
+#pragma unroll
+            for (int m = 0; m < kRows; ++m) {
+                const int i = part + m * parts;
+                if (i < dim) {
+                    S[m] *= kg[i];
+                    dot = fmaf(S[m], kk[i], dot);
+                }
+            }
+            for (int offset = parts >> 1; offset > 0; offset >>= 1) {
+                dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+            }
+            const float u = sb[c] * ((active ? sv[c * cols + col] : 0.0f) - dot);
+            float o = 0.0f;
+#pragma unroll
+            for (int m = 0; m < kRows; ++m) {
+                const int i = part + m * parts;
+                if (i < dim) {
+                    S[m] = fmaf(kk[i], u, S[m]);
+                    o = fmaf(S[m], kq[i], o);
+                }
+            }
+            for (int offset = parts >> 1; offset > 0; offset >>= 1) {
+                o += __shfl_xor_sync(0xffffffffu, o, offset);
+            }
+            if (active && part == 0) {
+                p.o_raw[(t0 + c) * (static_cast<int64_t>(p.n_heads) * p.vdim) + static_cast<int64_t>(head) * p.vdim +
+                        col0 + col] = o;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < kRows; ++m) {
+        const int i = part + m * parts;
+        if (active && i < dim) {
+            mine[static_cast<int64_t>(i) * p.vdim + col] = S[m];
+        }
+    }
+}
+
+// A warp per (token, head): the head's norm over vdim, its weight and the gate.
+template <typename scalar_t>
+__global__ void gated_delta_finish_kernel(const float* __restrict__ o_raw, const float* __restrict__ norm,
+                                          const scalar_t* __restrict__ gate_pre, int64_t gate_stride,
+                                          scalar_t* __restrict__ out, int64_t out_stride, int n_pairs, int n_heads,
+                                          int vdim, float eps) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    const int lane = threadIdx.x & 31;
+    const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= n_pairs) {
+        return;
+    }
+    const int64_t t = pair / n_heads;
+    const int h = pair % n_heads;
+    const float* o = o_raw + static_cast<int64_t>(pair) * vdim;
+    float square = 0.0f;
+    for (int d = lane; d < vdim; d += 32) {
+        square = fmaf(o[d], o[d], square);
+    }
+    square = pl_warp_sum(square);
+    const float factor = 1.0f / sqrtf(square / static_cast<float>(vdim) + eps);
+    for (int d = lane; d < vdim; d += 32) {
+        const float gate = 1.0f / (1.0f + expf(-pl_load(gate_pre + t * gate_stride + static_cast<int64_t>(h) * vdim + d)));
+        pl_store(out + t * out_stride + static_cast<int64_t>(h) * vdim + d, o[d] * factor * norm[d] * gate);
+    }
+}
+
+}  // namespace
+
+// q, k [T, qk_heads * dim] and v [T, n_heads * vdim] with qkv_stride elements between rows; b_pre
+// [T, n_heads]; a_pre [T, n_heads * dim]; gate_pre [T, n_heads * vdim]; a_log fp32 [n_heads]; dt_bias
+// fp32 [n_heads * dim]; norm fp32 [vdim]; state fp32 [slots, n_heads, dim, vdim] (updated); first_rows,
+// counts, slots int32 [entries]; o_raw fp32 [T, n_heads * vdim] scratch; out [T, n_heads * vdim].
+PL_API int pl_gated_delta(const void* q, const void* k, const void* v, int64_t qkv_stride, const void* b_pre,
+                          int64_t b_stride, const void* a_pre, int64_t a_stride, const void* gate_pre,
+                          int64_t gate_stride, const float* a_log, const float* dt_bias, const float* norm,
+                          float* state, const int32_t* first_rows, const int32_t* counts, const int32_t* slots,
+                          float* o_raw, void* out, int64_t out_stride, int n_tokens, int n_entries, int n_heads,
+                          int qk_heads, int dim, int vdim, float unit_eps, float q_scale, float eps, int dtype,
+                          cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && n_entries >= 0 && n_heads > 0 && qk_heads > 0 && dim > 0 && vdim > 0,
+               "gated_delta: bad sizes tokens=%d entries=%d heads=%d qk_heads=%d dim=%d vdim=%d", n_tokens, n_entries,
+               n_heads, qk_heads, dim, vdim);
+    PL_REQUIRE(n_heads % qk_heads == 0, "gated_delta: %d heads are not a multiple of %d q/k heads", n_heads, qk_heads);
+    PL_REQUIRE(dim <= 32 * kRows, "gated_delta: key size %d exceeds the supported maximum %d", dim, 32 * kRows);
+    PL_REQUIRE(n_heads <= 65535, "gated_delta: %d heads exceed the grid limit", n_heads);
+    if (n_tokens == 0 || n_entries == 0) {
+        return 0;
+    }
+    int parts = 1;
+    while (parts * kRows < dim) {
+        parts *= 2;
+    }
+    int cols = 128 / parts;
+    if (cols > vdim) {
+        cols = vdim;
+    }
+    int threads = ((cols * parts + 31) / 32) * 32;
+    int chunk = kChunkMost;
+    while (chunk > 1 && static_cast<size_t>(chunk) * (3 * dim + cols + 3) * sizeof(float) > 40 * 1024) {
+        chunk /= 2;
+    }
+    const size_t smem = static_cast<size_t>(chunk) * (3 * dim + cols + 3) * sizeof(float);
+    GatedDeltaParams p;
+    p.q = q; p.k = k; p.v = v; p.qkv_stride = qkv_stride; p.b_pre = b_pre; p.b_stride = b_stride; p.a_pre = a_pre;
+    p.a_stride = a_stride; p.a_log = a_log; p.dt_bias = dt_bias; p.state = state; p.first_rows = first_rows;
+    p.counts = counts; p.slots = slots; p.o_raw = o_raw; p.n_heads = n_heads; p.qk_heads = qk_heads; p.dim = dim;
+    p.vdim = vdim; p.parts = parts; p.cols = cols; p.chunk = chunk; p.unit_eps = unit_eps; p.q_scale = q_scale;
+    const dim3 grid(n_entries, n_heads, (vdim + cols - 1) / cols);
+    const int n_pairs = n_tokens * n_heads;
+    PL_DISPATCH_DTYPE(dtype, "gated_delta", {
+        pl_launch_overlapped(gated_delta_scan_kernel<scalar_t>, grid, dim3(threads), smem, stream, p);
+        pl_launch_overlapped(gated_delta_finish_kernel<scalar_t>, dim3((n_pairs + 3) / 4), dim3(128), 0, stream,
+                             static_cast<const float*>(o_raw), norm, static_cast<const scalar_t*>(gate_pre), gate_stride,
+                             static_cast<scalar_t*>(out), out_stride, n_pairs, n_heads, vdim, eps);
+    });
+    PL_CHECK_LAUNCH("gated_delta");
+    return 0;
+}

@@ -2,6 +2,10 @@
 //
 //   out[t, c] = h[t, c] + sum_{j < taps} w[c, j] * h_seq[t - (taps - 1) + j, c]
 //
+// or, for a mixer that filters its projections (pl_short_conv_act), without the input added
+// and with an activation: out = act(conv), act = silu or none; the rows of h may then be
+// columns of a wider matrix (h_stride elements between rows).
+//
 // where h_seq is the sequence's input so far, zeros before its start. A step brings a
 // sequence's next rows (an entry's rows are consecutive and in order); the taps - 1 inputs
 // before them come from the sequence's state slot [taps - 1, width] (oldest first), which
@@ -14,11 +18,22 @@ namespace {
 
 constexpr int kMaxTaps = 16;
 
+// What a row stores: the convolution added to its input, or the convolution alone, then the
+// activation (1: silu, z * sigmoid(z), with expf).
+__device__ __forceinline__ float conv_result(float own, float acc, int residual, int act) {
+    const float z = residual ? own + acc : acc;
+    return act == 1 ? z / (1.0f + expf(-z)) : z;
+}
+__device__ __forceinline__ float4 conv_result(float4 own, float4 acc, int residual, int act) {
+    return make_float4(conv_result(own.x, acc.x, residual, act), conv_result(own.y, acc.y, residual, act),
+                       conv_result(own.z, acc.z, residual, act), conv_result(own.w, acc.w, residual, act));
+}
+
 template <typename scalar_t>
 __global__ void short_conv_kernel(const scalar_t* __restrict__ h, const float* __restrict__ weight,
                                   const scalar_t* __restrict__ state, const int32_t* __restrict__ entry,
                                   const int32_t* __restrict__ slots, scalar_t* __restrict__ out, int n_tokens,
-                                  int width, int taps, int vectors) {
+                                  int width, int taps, int vectors, int64_t h_stride, int residual, int act) {
     pl_grid_trigger();
     pl_grid_wait();
     const int t = blockIdx.x;
@@ -33,7 +48,7 @@ __global__ void short_conv_kernel(const scalar_t* __restrict__ h, const float* _
     if (vectors) {
         // Four channels per thread, 8- or 16-byte loads (the width is a multiple of 4 and rows start on 16 bytes).
         for (int c = 4 * threadIdx.x; c < width; c += 4 * blockDim.x) {
-            const float4 own = pl_load4(h + static_cast<int64_t>(t) * width + c);
+            const float4 own = pl_load4(h + static_cast<int64_t>(t) * h_stride + c);
             float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             for (int j = 0; j < taps; ++j) {
                 const int back = reach - j;
@@ -41,7 +56,7 @@ __global__ void short_conv_kernel(const scalar_t* __restrict__ h, const float* _
                 if (back == 0) {
                     v = own;
                 } else if (back <= inside) {
-                    v = pl_load4(h + static_cast<int64_t>(t - back) * width + c);
+                    v = pl_load4(h + static_cast<int64_t>(t - back) * h_stride + c);
                 } else {
                     v = pl_load4(old + static_cast<int64_t>(reach - (back - inside)) * width + c);
                 }
@@ -50,14 +65,13 @@ __global__ void short_conv_kernel(const scalar_t* __restrict__ h, const float* _
                 acc.z = fmaf(weight[static_cast<int64_t>(c + 2) * taps + j], v.z, acc.z);
                 acc.w = fmaf(weight[static_cast<int64_t>(c + 3) * taps + j], v.w, acc.w);
             }
-            pl_store4(out + static_cast<int64_t>(t) * width + c,
-                      make_float4(own.x + acc.x, own.y + acc.y, own.z + acc.z, own.w + acc.w));
+            pl_store4(out + static_cast<int64_t>(t) * width + c, conv_result(own, acc, residual, act));
         }
         return;
     }
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         const float* w = weight + static_cast<int64_t>(c) * taps;
-        const float own = pl_load(h + static_cast<int64_t>(t) * width + c);
+        const float own = pl_load(h + static_cast<int64_t>(t) * h_stride + c);
         float acc = 0.0f;
         for (int j = 0; j < taps; ++j) {
             const int back = reach - j;  // this tap reads the input `back` rows before
@@ -65,13 +79,13 @@ __global__ void short_conv_kernel(const scalar_t* __restrict__ h, const float* _
             if (back == 0) {
                 v = own;
             } else if (back <= inside) {
-                v = pl_load(h + static_cast<int64_t>(t - back) * width + c);
+                v = pl_load(h + static_cast<int64_t>(t - back) * h_stride + c);
             } else {
                 v = pl_load(old + static_cast<int64_t>(reach - (back - inside)) * width + c);
             }
             acc = fmaf(w[j], v, acc);
         }
-        pl_store(out + static_cast<int64_t>(t) * width + c, own + acc);
+        pl_store(out + static_cast<int64_t>(t) * width + c, conv_result(own, acc, residual, act));
     }
 }
 
@@ -85,7 +99,7 @@ template <typename scalar_t, int TAPS>
 __global__ void __launch_bounds__(128) short_conv_rows_kernel(
         const scalar_t* __restrict__ h, const float* __restrict__ weight, const scalar_t* __restrict__ state,
         const int32_t* __restrict__ entry, const int32_t* __restrict__ slots, scalar_t* __restrict__ out, int n_tokens,
-        int width) {
+        int width, int64_t h_stride, int residual, int act) {
     pl_grid_trigger();
     constexpr int REACH = TAPS - 1;
     const int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
@@ -116,7 +130,7 @@ __global__ void __launch_bounds__(128) short_conv_rows_kernel(
 #pragma unroll
             for (int j = 0; j < REACH; ++j) {
                 const int back = REACH - j;
-                window[j] = back <= inside ? pl_load4(h + static_cast<int64_t>(t - back) * width + c)
+                window[j] = back <= inside ? pl_load4(h + static_cast<int64_t>(t - back) * h_stride + c)
                                            : pl_load4(old + static_cast<int64_t>(REACH - (back - inside)) * width + c);
             }
         } else if (e != last_entry) {
@@ -134,7 +148,7 @@ __global__ void __launch_bounds__(128) short_conv_rows_kernel(
                 window[REACH - 1] = last;
             }
         }
-        const float4 own = pl_load4(h + static_cast<int64_t>(t) * width + c);
+        const float4 own = pl_load4(h + static_cast<int64_t>(t) * h_stride + c);
         float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
         for (int j = 0; j < REACH; ++j) {
@@ -147,8 +161,7 @@ __global__ void __launch_bounds__(128) short_conv_rows_kernel(
         acc.y = fmaf(w[1][REACH], own.y, acc.y);
         acc.z = fmaf(w[2][REACH], own.z, acc.z);
         acc.w = fmaf(w[3][REACH], own.w, acc.w);
-        pl_store4(out + static_cast<int64_t>(t) * width + c,
-                  make_float4(own.x + acc.x, own.y + acc.y, own.z + acc.z, own.w + acc.w));
+        pl_store4(out + static_cast<int64_t>(t) * width + c, conv_result(own, acc, residual, act));
         last = own;
         last_entry = e;
     }
@@ -160,7 +173,7 @@ __global__ void __launch_bounds__(128) short_conv_rows_kernel(
 template <typename scalar_t>
 __global__ void short_conv_state_kernel(const scalar_t* __restrict__ h, const int32_t* __restrict__ entry,
                                         const int32_t* __restrict__ slots, scalar_t* __restrict__ state,
-                                        int n_tokens, int width, int taps) {
+                                        int n_tokens, int width, int taps, int64_t h_stride) {
     pl_grid_trigger();
     pl_grid_wait();
     const int t = blockIdx.x;
@@ -179,7 +192,7 @@ __global__ void short_conv_state_kernel(const scalar_t* __restrict__ h, const in
         // A portion of at least `reach` rows: each of its last `reach` rows writes itself.
         if (after < reach) {
             for (int c = threadIdx.x; c < width; c += blockDim.x) {
-                mine[static_cast<int64_t>(reach - 1 - after) * width + c] = h[static_cast<int64_t>(t) * width + c];
+                mine[static_cast<int64_t>(reach - 1 - after) * width + c] = h[static_cast<int64_t>(t) * h_stride + c];
             }
         }
         return;
@@ -194,7 +207,7 @@ __global__ void short_conv_state_kernel(const scalar_t* __restrict__ h, const in
             mine[static_cast<int64_t>(j) * width + c] = mine[static_cast<int64_t>(j + n) * width + c];
         }
         for (int m = 0; m < n; ++m) {
-            mine[static_cast<int64_t>(reach - n + m) * width + c] = h[static_cast<int64_t>(t + m) * width + c];
+            mine[static_cast<int64_t>(reach - n + m) * width + c] = h[static_cast<int64_t>(t + m) * h_stride + c];
         }
     }
 }
@@ -204,22 +217,22 @@ __global__ void short_conv_state_kernel(const scalar_t* __restrict__ h, const in
 // h, out [T, width] and state [slots, taps - 1, width] in the engine's dtype; weight fp32
 // [width, taps]; entry int32 [T] names each row's batch entry, slots int32 [entries] each
 // entry's state slot. out may not alias h. The state is read, not written.
-PL_API int pl_short_conv(const void* h, const float* weight, const void* state, const int32_t* entry,
-                         const int32_t* slots, void* out, int n_tokens, int width, int taps, int dtype,
-                         cudaStream_t stream) {
+static int short_conv_launch(const void* h, int64_t h_stride, const float* weight, const void* state,
+                             const int32_t* entry, const int32_t* slots, void* out, int n_tokens, int width, int taps,
+                             int residual, int act, int dtype, cudaStream_t stream) {
     PL_REQUIRE(n_tokens >= 0 && width > 0 && taps >= 1 && taps <= kMaxTaps, "short_conv: bad sizes tokens=%d width=%d "
                "taps=%d (at most %d)", n_tokens, width, taps, kMaxTaps);
     if (n_tokens == 0) {
         return 0;
     }
-    const int vectors = width % 4 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(state) |
-                                            reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int vectors = width % 4 == 0 && h_stride % 4 == 0 &&
+        ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     if (vectors && taps >= 2 && taps <= 6) {
         const dim3 grid((n_tokens + kRowsPerBlock - 1) / kRowsPerBlock, (width / 4 + 127) / 128);
 #define PL_CONV_ROWS(T)                                                                                          \
     pl_launch_overlapped(short_conv_rows_kernel<scalar_t, T>, grid, dim3(128), 0, stream,                        \
                          static_cast<const scalar_t*>(h), weight, static_cast<const scalar_t*>(state), entry,    \
-                         slots, static_cast<scalar_t*>(out), n_tokens, width)
+                         slots, static_cast<scalar_t*>(out), n_tokens, width, h_stride, residual, act)
         if (dtype == PL_F32) {
             using scalar_t = float;
             switch (taps) {
@@ -250,16 +263,39 @@ PL_API int pl_short_conv(const void* h, const float* weight, const void* state, 
     PL_DISPATCH_DTYPE(dtype, "short_conv", {
         pl_launch_overlapped(short_conv_kernel<scalar_t>, dim3(n_tokens), dim3(threads), 0, stream,
                              static_cast<const scalar_t*>(h), weight, static_cast<const scalar_t*>(state), entry, slots,
-                             static_cast<scalar_t*>(out), n_tokens, width, taps, vectors);
+                             static_cast<scalar_t*>(out), n_tokens, width, taps, vectors, h_stride, residual, act);
     });
     PL_CHECK_LAUNCH("short_conv");
     return 0;
 }
 
+PL_API int pl_short_conv(const void* h, const float* weight, const void* state, const int32_t* entry,
+                         const int32_t* slots, void* out, int n_tokens, int width, int taps, int dtype,
+                         cudaStream_t stream) {
+    return short_conv_launch(h, width, weight, state, entry, slots, out, n_tokens, width, taps, 1, 0, dtype, stream);
+}
+
+// The same with the rows of h `h_stride` elements apart, the input added only when `residual`,
+// and an activation on the result (0: none, 1: silu). out [T, width] is contiguous.
+PL_API int pl_short_conv_act(const void* h, int64_t h_stride, const float* weight, const void* state,
+                             const int32_t* entry, const int32_t* slots, void* out, int n_tokens, int width, int taps,
+                             int residual, int act, int dtype, cudaStream_t stream) {
+    PL_REQUIRE(act == 0 || act == 1, "short_conv: unknown activation code %d", act);
+    PL_REQUIRE(h_stride >= width, "short_conv: rows of %d columns cannot be %lld elements apart", width,
+               static_cast<long long>(h_stride));
+    return short_conv_launch(h, h_stride, weight, state, entry, slots, out, n_tokens, width, taps, residual, act,
+                             dtype, stream);
+}
+
 // Brings every entry's state slot up to date with the step's inputs h (run after
 // pl_short_conv has read the old state).
 PL_API int pl_short_conv_state(const void* h, const int32_t* entry, const int32_t* slots, void* state, int n_tokens,
-                               int width, int taps, int dtype, cudaStream_t stream) {
+                               int width, int taps, int dtype, cudaStream_t stream);
+
+// (h_stride: elements between the rows of h)
+PL_API int pl_short_conv_state_strided(const void* h, int64_t h_stride, const int32_t* entry, const int32_t* slots,
+                                       void* state, int n_tokens, int width, int taps, int dtype,
+                                       cudaStream_t stream) {
     PL_REQUIRE(n_tokens >= 0 && width > 0 && taps >= 1 && taps <= kMaxTaps, "short_conv_state: bad sizes tokens=%d "
                "width=%d taps=%d", n_tokens, width, taps);
     if (n_tokens == 0 || taps == 1) {
@@ -269,8 +305,13 @@ PL_API int pl_short_conv_state(const void* h, const int32_t* entry, const int32_
     PL_DISPATCH_DTYPE(dtype, "short_conv_state", {
         pl_launch_overlapped(short_conv_state_kernel<scalar_t>, dim3(n_tokens), dim3(threads), 0, stream,
                              static_cast<const scalar_t*>(h), entry, slots, static_cast<scalar_t*>(state), n_tokens,
-                             width, taps);
+                             width, taps, h_stride);
     });
     PL_CHECK_LAUNCH("short_conv_state");
     return 0;
+}
+
+PL_API int pl_short_conv_state(const void* h, const int32_t* entry, const int32_t* slots, void* state, int n_tokens,
+                               int width, int taps, int dtype, cudaStream_t stream) {
+    return pl_short_conv_state_strided(h, width, entry, slots, state, n_tokens, width, taps, dtype, stream);
 }

@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 23
+ABI_VERSION = 24
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -84,6 +84,21 @@ _SIGNATURES = {
     "pl_gemm_bf16_pair": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _I32, _PTR, _PTR],
     "pl_attention_decode_resident_clusters": [_I32, _I32, _I32],
     "pl_gemm_bf16_skinny_splits": [_I32, _I32, _I32],
+    "pl_pair_residual_norm": [_PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _F32, _I32,
+                              _PTR],
+    "pl_rope_maps_write": [_PTR, _PTR, _PTR, _I64, _PTR, _PTR, _PTR, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR,
+                           _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _PTR, _I32, _PTR, _PTR],
+    "pl_diff_combine": [_PTR, _PTR, _I32, _I32, _I32, _I32, _F32, _F32, _F32, _I32, _PTR],
+    "pl_short_conv_act": [_PTR, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
+    "pl_short_conv_state_strided": [_PTR, _I64, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
+    "pl_gated_delta": [_PTR, _PTR, _PTR, _I64, _PTR, _I64, _PTR, _I64, _PTR, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR,
+                       _PTR, _PTR, _PTR, _I64, _I32, _I32, _I32, _I32, _I32, _I32, _F32, _F32, _F32, _I32, _PTR],
+    "pl_moe_route": [_PTR, _I64, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
+    "pl_moe_gate_up": [_PTR, _I64, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
+    "pl_moe_down": [_PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
+    "pl_moe_sort": [_PTR, _I32, _I32, _PTR, _PTR, _PTR, _PTR],
+    "pl_moe_gather": [_PTR, _I64, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
+    "pl_moe_combine": [_PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
     "pl_sample": [_PTR, _I64, _I32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
 }
 
@@ -339,6 +354,204 @@ def delta_rule(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tenso
           n_entries, n_heads, dim, float(decay_scale), float(unit_eps), float(eps), _code(out.dtype), _stream())
     global _launches
     _launches += 1  # (two kernels)
+
+
+def pair_residual_norm(x: torch.Tensor, y1: torch.Tensor | None, s1: torch.Tensor | None, y2: torch.Tensor | None,
+                       s2: torch.Tensor | None, also: torch.Tensor | None, w1: torch.Tensor | None,
+                       w2: torch.Tensor | None, h1: torch.Tensor | None, h2: torch.Tensor | None, eps: float,
+                       rows: torch.Tensor | None = None) -> None:
+    """x += s1 * y1 + s2 * y2 + also (each optional), then h1 = rmsnorm(x) * w1 and h2 = rmsnorm(x) * w2
+    (see csrc/parallel_norm.cu). x fp32 [T, H]; y1, y2, h1, h2 in the engine's dtype; s1, s2, w1, w2, also
+    fp32. With `rows` only those rows are normed and x is left as it is."""
+    _dev(x, y1, s1, y2, s2, also, w1, w2, h1, h2, rows)
+    tokens, hidden = x.shape
+    outs = [h for h in (h1, h2) if h is not None]
+    assert outs and x.dtype == torch.float32 and x.is_contiguous()
+    dtype = outs[0].dtype
+    n_rows = rows.numel() if rows is not None else tokens
+    for y in (y1, y2):
+        assert y is None or (y.shape == (tokens, hidden) and y.is_contiguous() and y.dtype == dtype)
+    for v in (s1, s2, w1, w2):
+        assert v is None or (v.dtype == torch.float32 and v.shape == (hidden,) and v.is_contiguous())
+    assert also is None or (also.dtype == torch.float32 and also.shape == x.shape and also.is_contiguous())
+    for h in outs:
+        assert h.shape == (n_rows, hidden) and h.is_contiguous() and h.dtype == dtype
+    assert rows is None or rows.dtype == torch.int32
+    _call("pl_pair_residual_norm", _p(x), _p(y1), _p(s1), _p(y2), _p(s2), _p(also), _p(w1), _p(w2), _p(h1), _p(h2),
+          _p(rows), n_rows, hidden, float(eps), _code(dtype), _stream())
+
+
+def rope_maps_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: torch.Tensor, entry: torch.Tensor,
+                    table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_size: int,
+                    inv_freq: torch.Tensor | None, rotary: int, n_heads: int, n_kv_heads: int, maps: int, dim: int,
+                    vdim: int, q_out: torch.Tensor, status: torch.Tensor | None) -> None:
+    """Lays the score maps of every head out as heads of their own, rotates q and k (neighbouring
+    pairs within each map's first `rotary` columns) and writes k and v rows into their pages (see
+    csrc/rope_maps.cu). q [T, heads * maps * dim], k [T, kv_heads * maps * dim], v [T, kv_heads * vdim]
+    with one row stride; q_out [T, heads * maps, padded]; pools [pages, kv_heads, page_size, padded]."""
+    _dev(q, k, v, pos, entry, table, k_pool, v_pool, inv_freq, q_out, status)
+    tokens = q.shape[0]
+    padded = q_out.shape[2]
+    assert q.shape[1] == n_heads * maps * dim and k.shape[1] == n_kv_heads * maps * dim and v.shape[1] == n_kv_heads * vdim
+    assert q.stride(1) == k.stride(1) == v.stride(1) == 1 and q.stride(0) == k.stride(0) == v.stride(0)
+    assert q_out.is_contiguous() and q_out.shape == (tokens, n_heads * maps, padded) and q_out.dtype == q.dtype
+    assert k_pool.dtype == q.dtype and k_pool.shape[1:] == (n_kv_heads, page_size, padded) and v_pool.shape == k_pool.shape
+    assert k_pool.stride() == v_pool.stride() and k_pool.stride(3) == 1 and k_pool.stride(2) == padded
+    assert inv_freq is None or (inv_freq.dtype == torch.float64 and inv_freq.numel() == rotary // 2)
+    _call("pl_rope_maps_write", _p(q), _p(k), _p(v), q.stride(0), _p(pos), _p(entry), _p(table), table.shape[1],
+          _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1), page_size, k_pool.shape[0], _p(inv_freq),
+          rotary if inv_freq is not None else 0, tokens, n_heads, n_kv_heads, maps, dim, vdim, padded, _p(q_out),
+          _code(q.dtype), _p(status), _stream())
+
+
+def diff_combine(a: torch.Tensor, out: torch.Tensor, n_heads: int, vdim: int, lam: float, eps: float,
+                 mult: float) -> None:
+    """out[t, h] = mult * unit_rms(a[t, h, 0] - lam * a[t, h, 1]) over the first vdim columns; a [T, heads * 2,
+    padded], out [T, heads * vdim]."""
+    _dev(a, out)
+    tokens, rows, padded = a.shape
+    assert rows == 2 * n_heads and a.is_contiguous() and out.is_contiguous() and out.shape == (tokens, n_heads * vdim)
+    assert a.dtype == out.dtype
+    _call("pl_diff_combine", _p(a), _p(out), tokens, n_heads, vdim, padded, float(lam), float(eps), float(mult),
+          _code(a.dtype), _stream())
+
+
+def short_conv_act(h: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, entry: torch.Tensor,
+                   slots: torch.Tensor, out: torch.Tensor, residual: bool, act: str) -> None:
+    """out = act(conv(h) [+ h]) per channel over time; h [T, W] may be columns of a wider matrix (unit column
+    stride); act "none" or "silu". The state [slots, taps - 1, W] is read only."""
+    _dev(h, weight, state, entry, slots, out)
+    tokens, width = h.shape
+    taps = weight.shape[1]
+    assert weight.dtype == torch.float32 and weight.shape == (width, taps) and weight.is_contiguous()
+    assert h.stride(1) == 1 and out.is_contiguous() and out.shape == h.shape and out.dtype == h.dtype == state.dtype
+    assert state.is_contiguous() and state.shape[1:] == (taps - 1, width) and out.data_ptr() != h.data_ptr()
+    _call("pl_short_conv_act", _p(h), h.stride(0) if tokens > 1 else width, _p(weight), _p(state), _p(entry),
+          _p(slots), _p(out), tokens, width, taps, int(bool(residual)), {"none": 0, "silu": 1}[act], _code(h.dtype),
+          _stream())
+
+
+def short_conv_state_strided(h: torch.Tensor, entry: torch.Tensor, slots: torch.Tensor, state: torch.Tensor) -> None:
+    """short_conv_state for rows of h that are columns of a wider matrix."""
+    _dev(h, entry, slots, state)
+    tokens, width = h.shape
+    taps = state.shape[1] + 1
+    assert h.stride(1) == 1 and state.is_contiguous() and state.dtype == h.dtype and state.shape[2] == width
+    _call("pl_short_conv_state_strided", _p(h), h.stride(0) if tokens > 1 else width, _p(entry), _p(slots), _p(state),
+          tokens, width, taps, _code(h.dtype), _stream())
+
+
+def gated_delta(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b_pre: torch.Tensor, a_pre: torch.Tensor,
+                gate_pre: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, norm: torch.Tensor,
+                state: torch.Tensor, first_rows: torch.Tensor, counts: torch.Tensor, slots: torch.Tensor,
+                out: torch.Tensor, n_heads: int, qk_heads: int, dim: int, vdim: int, unit_eps: float, q_scale: float,
+                eps: float) -> None:
+    """The gated delta rule with a decay per key channel over each entry's rows in order (see
+    csrc/gated_delta.cu). q, k [T, qk_heads * dim] and v [T, heads * vdim] share one row stride; state fp32
+    [slots, heads, dim, vdim] is updated."""
+    _dev(q, k, v, b_pre, a_pre, gate_pre, a_log, dt_bias, norm, state, first_rows, counts, slots, out)
+    tokens = q.shape[0]
+    assert q.shape[1] == k.shape[1] == qk_heads * dim and v.shape[1] == n_heads * vdim
+    assert q.stride(0) == k.stride(0) == v.stride(0) and q.stride(1) == k.stride(1) == v.stride(1) == 1
+    for t, width in ((b_pre, n_heads), (a_pre, n_heads * dim), (gate_pre, n_heads * vdim), (out, n_heads * vdim)):
+        assert t.shape == (tokens, width) and t.stride(1) == 1 and t.dtype == q.dtype
+    assert a_log.dtype == dt_bias.dtype == norm.dtype == torch.float32
+    assert a_log.shape == (n_heads,) and dt_bias.shape == (n_heads * dim,) and norm.shape == (vdim,)
+    assert a_log.is_contiguous() and dt_bias.is_contiguous() and norm.is_contiguous()
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (n_heads, dim, vdim)
+    n_entries = first_rows.numel()
+    assert counts.numel() == n_entries and slots.numel() >= n_entries
+    o_raw = torch.empty((tokens, n_heads * vdim), dtype=torch.float32, device=out.device)
+
+    def stride(t):
+        return t.stride(0) if tokens > 1 else t.shape[1]
+
+    _call("pl_gated_delta", _p(q), _p(k), _p(v), stride(q), _p(b_pre), stride(b_pre), _p(a_pre), stride(a_pre),
+          _p(gate_pre), stride(gate_pre), _p(a_log), _p(dt_bias), _p(norm), _p(state), _p(first_rows), _p(counts),
+          _p(slots), _p(o_raw), _p(out), stride(out), tokens, n_entries, n_heads, qk_heads, dim, vdim, float(unit_eps),
+          float(q_scale), float(eps), _code(out.dtype), _stream())
+    global _launches
+    _launches += 1  # (two kernels)
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, top: int, n_groups: int,
+              keep: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """(ids int32 [T, top], weights fp32 [T, top]) of the experts each token's router chooses (see csrc/moe.cu)."""
+    _dev(h, router, correction)
+    tokens, hidden = h.shape
+    n_experts = router.shape[0]
+    assert router.dtype == torch.float32 and router.shape == (n_experts, hidden) and router.is_contiguous()
+    assert correction is None or (correction.dtype == torch.float32 and correction.shape == (n_experts,))
+    assert h.stride(1) == 1
+    ids = torch.empty((tokens, top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=h.device)
+    _call("pl_moe_route", _p(h), h.stride(0) if tokens > 1 else hidden, _p(router), _p(correction), _p(ids),
+          _p(weights), tokens, hidden, n_experts, top, n_groups, keep, _code(h.dtype), _stream())
+    return ids, weights
+
+
+def moe_gate_up(h: torch.Tensor, gate_up: torch.Tensor, ids: torch.Tensor, act: torch.Tensor) -> None:
+    """act[t * top + j] = silu(Wg h_t) * (Wu h_t) with the weights of expert ids[t, j]; gate_up [E, 2 * ff, H]."""
+    _dev(h, gate_up, ids, act)
+    tokens, hidden = h.shape
+    n_experts, two_ff, _ = gate_up.shape
+    top = ids.shape[1]
+    assert gate_up.is_contiguous() and gate_up.shape[2] == hidden and gate_up.dtype == h.dtype == act.dtype
+    assert act.is_contiguous() and act.shape == (tokens * top, two_ff // 2) and ids.is_contiguous() and h.stride(1) == 1
+    _call("pl_moe_gate_up", _p(h), h.stride(0) if tokens > 1 else hidden, _p(gate_up), _p(ids), _p(act), tokens,
+          hidden, two_ff // 2, top, n_experts, _code(h.dtype), _stream())
+
+
+def moe_down(act: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+             also: torch.Tensor | None, out: torch.Tensor) -> None:
+    """out[t] = sum_j weights[t, j] * W_down,ids[t, j] act[t * top + j] + also[t]; down [E, H, ff]."""
+    _dev(act, down, ids, weights, also, out)
+    tokens, hidden = out.shape
+    n_experts, _, ff = down.shape
+    top = ids.shape[1]
+    assert down.is_contiguous() and down.shape[1] == hidden and down.dtype == act.dtype == out.dtype
+    assert act.is_contiguous() and act.shape == (tokens * top, ff) and out.is_contiguous()
+    assert weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape == ids.shape
+    assert also is None or (also.shape == out.shape and also.is_contiguous() and also.dtype == out.dtype)
+    _call("pl_moe_down", _p(act), _p(down), _p(ids), _p(weights), _p(also), _p(out), tokens, hidden, ff, top,
+          n_experts, _code(out.dtype), _stream())
+
+
+def moe_sort(ids: torch.Tensor, n_experts: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The (token, expert) pairs in expert order: (ends int32 [E]: the row after each expert's last,
+    row_of_pair int32 [pairs], pair_of_row int32 [pairs])."""
+    _dev(ids)
+    pairs = ids.numel()
+    assert ids.dtype == torch.int32 and ids.is_contiguous()
+    ends = torch.empty(n_experts, dtype=torch.int32, device=ids.device)
+    row_of_pair = torch.empty(pairs, dtype=torch.int32, device=ids.device)
+    pair_of_row = torch.empty(pairs, dtype=torch.int32, device=ids.device)
+    _call("pl_moe_sort", _p(ids), pairs, n_experts, _p(ends), _p(row_of_pair), _p(pair_of_row), _stream())
+    return ends, row_of_pair, pair_of_row
+
+
+def moe_gather(x: torch.Tensor, pair_of_row: torch.Tensor, top: int) -> torch.Tensor:
+    """Rows of x in expert order: out[r] = x[pair_of_row[r] // top]."""
+    _dev(x, pair_of_row)
+    assert x.stride(1) == 1
+    pairs = pair_of_row.numel()
+    out = torch.empty((pairs, x.shape[1]), dtype=x.dtype, device=x.device)
+    _call("pl_moe_gather", _p(x), x.stride(0) if x.shape[0] > 1 else x.shape[1], _p(pair_of_row), _p(out), pairs,
+          x.shape[1], top, _code(x.dtype), _stream())
+    return out
+
+
+def moe_combine(y: torch.Tensor, row_of_pair: torch.Tensor, weights: torch.Tensor, also: torch.Tensor | None,
+                out: torch.Tensor) -> None:
+    """out[t] = sum_j weights[t, j] * y[row_of_pair[t * top + j]] + also[t]."""
+    _dev(y, row_of_pair, weights, also, out)
+    tokens, hidden = out.shape
+    top = weights.shape[1]
+    assert y.is_contiguous() and y.shape == (tokens * top, hidden) and y.dtype == out.dtype and out.is_contiguous()
+    assert weights.dtype == torch.float32 and weights.is_contiguous()
+    assert also is None or (also.shape == out.shape and also.is_contiguous() and also.dtype == out.dtype)
+    _call("pl_moe_combine", _p(y), _p(row_of_pair), _p(weights), _p(also), _p(out), tokens, hidden, top,
+          _code(out.dtype), _stream())
 
 
 def norm_write_paged(z: torch.Tensor, weight: torch.Tensor, eps: float, pos: torch.Tensor, entry: torch.Tensor,

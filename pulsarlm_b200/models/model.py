@@ -117,6 +117,14 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, self.ctx)
         self.head = build_part("head", spec.head, self.ctx)
         self.loaded = False
+        # The cache units, in the order the cache manager hears of them: one per layer, or
+        # (spec.cache_per_run) one per entry of the order. `_unit_layer[u]` is the layer of unit u.
+        self._unit_layer = list(spec.order) if spec.cache_per_run else list(range(len(spec.layers)))
+        self._run_bindings: list | None = None
+        self._rejoin = frozenset(int(r) for r in spec.rejoin_runs)
+        for r in self._rejoin:
+            if not 0 < r < len(spec.order):
+                raise ValueError(f"the embedding cannot rejoin the stream before run {r} of {len(spec.order)}")
 
     # ------------------------------------------------------------------ weights
     def tensor_needs(self) -> dict[str, TensorNeed]:
@@ -142,7 +150,8 @@ class Model:
         """Per layer: the mixer's KVCacheNeed, StateNeed or None; for a block whose other
         parts keep state too (`cache_holders()`), a tuple with every holder's need."""
         out = []
-        for b in self.blocks:
+        for layer in self._unit_layer:
+            b = self.blocks[layer]
             holders = getattr(b, "cache_holders", None)
             out.append(tuple(h.cache_need() for h in holders()) if holders is not None else b.mixer.cache_need())
         return out
@@ -151,8 +160,8 @@ class Model:
         """The part behind a cache manager's holder key: a layer's mixer, or for the key
         (layer, place) that place among the block's cache holders."""
         if isinstance(key, tuple):
-            return self.blocks[key[0]].cache_holders()[key[1]]
-        return self.blocks[key].mixer
+            return self.blocks[self._unit_layer[key[0]]].cache_holders()[key[1]]
+        return self.blocks[self._unit_layer[key]].mixer
 
     def cache_sources(self) -> list[int | None]:
         """Per layer: the layer whose cache it reads instead of its own, or None."""
@@ -192,7 +201,28 @@ class Model:
                 seen[key] = part
         return list(seen.items())
 
+    def _bind_block(self, b, mine) -> None:
+        if hasattr(b, "cache_holders"):
+            for holder, binding in zip(b.cache_holders(), mine):
+                if binding is not None:
+                    holder.bind_cache(binding)
+        elif mine is not None:
+            b.mixer.bind_cache(mine[0] if isinstance(mine, list) else mine)
+
     def bind_caches(self, bindings: list) -> None:
+        if self.spec.cache_per_run:
+            # One binding per run: a block is pointed at its run's cache right before it runs
+            # (`forward`); here each block gets the binding of its first run, so that whatever the
+            # parts derive from a binding (page size, kernels' shapes) is known before a step.
+            if any(getattr(b.mixer, "cache_from", None) is not None for b in self.blocks):
+                raise ValueError("a model that keeps a cache per run cannot have layers that read another's cache")
+            self._run_bindings = list(bindings)
+            seen = set()
+            for run, layer in enumerate(self.spec.order):
+                if layer not in seen:
+                    seen.add(layer)
+                    self._bind_block(self.blocks[layer], bindings[run])
+            return
         sources = self.cache_sources()
         for layer, b in enumerate(self.blocks):
             src = sources[layer] if sources[layer] is not None else layer
@@ -208,6 +238,15 @@ class Model:
                 theirs = bindings[src]
                 b.mixer.bind_cache(theirs[0] if isinstance(theirs, list) else theirs)
 
+    @staticmethod
+    def _rejoin_stream(x, delta, entered):
+        """The embedding's output enters the stream again: with the pending output where its kind
+        can carry a row of its own (the next norm's kernel then adds it in the same pass), else now."""
+        if delta is not None and hasattr(delta, "with_also"):
+            return x, delta.with_also(entered)
+        x.add_(entered)
+        return x, delta
+
     # ------------------------------------------------------------------ forward
     def forward(self, batch: StepBatch) -> torch.Tensor | None:
         """Runs the batch's tokens through every layer in order; returns fp32 logits
@@ -216,8 +255,15 @@ class Model:
             raise RuntimeError("the model has no weights loaded")
         x = self.embedding.forward(batch.tokens, batch)
         delta = None
-        for index in self.spec.order:
-            x, delta = self.blocks[index].forward(x, delta, batch)
+        entered = x.clone() if self._rejoin else None  # (the stream is updated in place)
+        repeated = self._run_bindings is not None and len(self.spec.order) != len(set(self.spec.order))
+        for run, index in enumerate(self.spec.order):
+            block = self.blocks[index]
+            if repeated:
+                self._bind_block(block, self._run_bindings[run])
+            if run in self._rejoin:
+                x, delta = self._rejoin_stream(x, delta, entered)
+            x, delta = block.forward(x, delta, batch)
         if batch.want_rows is None or batch.want_rows.numel() == 0:
             return None
         h = self.final_norm.forward(x, delta, rows=batch.want_rows)

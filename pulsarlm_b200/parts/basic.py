@@ -31,27 +31,52 @@ class NormedDelta:
     bias: torch.Tensor | None = None
 
 
+@dataclasses.dataclass
+class ScaledPair:
+    """The outputs of two sublayers that read the same stream, each scaled per channel on
+    its way in: x += s1 * y1 + s2 * y2 (+ also). y2 / s2 are None for a layer with one
+    sublayer; s1 / s2 None means unscaled; `also` is an fp32 [T, H] row added too. A block
+    hands it on in the place of a plain delta; the next norm's kernel does the adds and its
+    own norm in one pass (ops.pair_residual_norm)."""
+
+    y1: torch.Tensor
+    s1: torch.Tensor | None
+    y2: torch.Tensor | None = None
+    s2: torch.Tensor | None = None
+    also: torch.Tensor | None = None
+
+    def with_also(self, rows: torch.Tensor) -> "ScaledPair":
+        if self.also is not None:
+            rows = self.also + rows
+        return dataclasses.replace(self, also=rows)
+
+
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
     """h = v * rsqrt(mean(v^2) + eps) * weight over the fp32 residual stream, with
     the pending layer output added first (v = x + delta, x updated in place; a
-    NormedDelta is normed and scaled on its way in).
-    params: hidden_size, eps. tensors: weight [hidden_size].
+    NormedDelta is normed and scaled on its way in, a ScaledPair scaled and added).
+    params: hidden_size, eps, unit_offset (optional: the stored weight is kept around
+    zero and the scale is 1 + weight, formed in fp32). tensors: weight [hidden_size].
     Formula: pulsarlm-core/src/kernels/rmsnorm.cu:29-49."""
 
     def __init__(self, spec: PartSpec, ctx: BuildContext):
         super().__init__(spec, ctx)
         self.hidden = int(self.param("hidden_size"))
         self.eps = float(self.param("eps"))
+        self.unit_offset = bool(spec.params.get("unit_offset", False))
         self.weight: torch.Tensor | None = None
 
     @classmethod
     def tensor_needs(cls, spec: PartSpec) -> dict[str, TensorNeed]:
-        return {spec.tensors["weight"]: TensorNeed((int(spec.params["hidden_size"]),), role="vector")}
+        role = "offset" if spec.params.get("unit_offset") else "vector"
+        return {spec.tensors["weight"]: TensorNeed((int(spec.params["hidden_size"]),), role=role)}
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         self.weight = tensors[self.spec.tensors["weight"]].contiguous()
         self._weight_f32: torch.Tensor | None = None
+        if self.unit_offset:
+            self.weight = self._weight_f32 = (self.weight.float() + 1.0).contiguous()
 
     def weight_f32(self) -> torch.Tensor:
         if self._weight_f32 is None:
@@ -64,7 +89,12 @@ class RMSNorm(Part):
         step's entries bring one token each)."""
         n = rows.numel() if rows is not None else x.shape[0]
         out = torch.empty((n, self.hidden), dtype=self.ctx.dtype, device=x.device)
-        if isinstance(delta, NormedDelta):
+        if isinstance(delta, ScaledPair):
+            if conv is not None:
+                raise ValueError("rmsnorm: a filter cannot ride along with a pair of scaled outputs")
+            ops.pair_residual_norm(x, delta.y1, delta.s1, delta.y2, delta.s2, delta.also, self.weight_f32(), None,
+                                   out, None, self.eps, rows)
+        elif isinstance(delta, NormedDelta):
             ops.add_normed_rmsnorm(x, delta.y, delta.weight, delta.mult, delta.eps, self.weight_f32(), self.eps, out,
                                    rows, delta.bias, conv)
         else:
@@ -115,6 +145,28 @@ class Rope(Part):
             raise ValueError(f"rope: rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         freqs = rope_inverse_frequencies(float(self.param("theta")), self.head_dim, self.rotary_dim,
                                          spec.params.get("llama3"))
+        self.inv_freq = torch.tensor(freqs, dtype=torch.float64, device=ctx.device)
+
+    def table(self) -> tuple[torch.Tensor | None, int]:
+        return (self.inv_freq if self.rotary_dim > 0 else None), self.rotary_dim
+
+
+@register_part("position", "rope_pairs")
+class RopePairs(Part):
+    """Rotary encoding over neighbouring pairs: within the first `rotary_dim` columns of a
+    vector, (2i, 2i + 1) turns by the angle pos * f_i with f_i = theta^(-2i / rotary_dim) /
+    factor (`factor`: linear position scaling, 1 when absent); the other columns pass through.
+    params: theta, rotary_dim (even), factor (optional). No tensors. `table()` gives the fp64
+    radians per position and the rotary width; the mixer's kernel decides what a vector is."""
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.rotary_dim = int(self.param("rotary_dim"))
+        if self.rotary_dim % 2 or self.rotary_dim < 0:
+            raise ValueError(f"rope_pairs: rotary_dim {self.rotary_dim} must be even and not negative")
+        theta = float(self.param("theta"))
+        factor = float(spec.params.get("factor") or 1.0)
+        freqs = [theta ** (-2.0 * i / self.rotary_dim) / factor for i in range(self.rotary_dim // 2)]
         self.inv_freq = torch.tensor(freqs, dtype=torch.float64, device=ctx.device)
 
     def table(self) -> tuple[torch.Tensor | None, int]:

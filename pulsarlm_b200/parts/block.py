@@ -10,7 +10,8 @@ from __future__ import annotations
 import torch
 
 from . import native_layer
-from .basic import NormedDelta
+from ..kernels import ops
+from .basic import NormedDelta, RMSNorm, ScaledPair
 from .registry import BuildContext, build_part, register_part
 from .spec import LayerSpec
 
@@ -131,3 +132,104 @@ class SandwichNormBlock:
         else:
             y = self.feed_forward.forward(h, batch)
         return x, self.ff_out_norm.pending(y, self.mult, bias)
+
+
+@register_part("block", "parallel")
+class ParallelBlock:
+    """Both sublayers read the same stream, each through a norm of its own, and their
+    outputs enter it together, each scaled per channel:
+
+        x += scale_mixer * mixer(norm_mixer(x)) + scale_ff * feed_forward(norm_ff(x))
+
+    Norm names in the LayerSpec: "mixer" and "feed_forward" (the latter only where the layer
+    has a feed-forward). `extras`: "mixer_scale" / "feed_forward_scale", checkpoint names of
+    the per-channel scales [hidden] (absent: unscaled). The sum is not formed here: the
+    outputs travel as a ScaledPair and the next block's norm kernel scales them, adds them
+    into the fp32 stream and writes both of its norms in one pass."""
+
+    def __init__(self, spec: LayerSpec, ctx: BuildContext):
+        self.spec = spec
+        self.ctx = ctx
+        extras = spec.extras or {}
+        self.mixer_norm = build_part("norm", spec.norms["mixer"], ctx)
+        self.mixer = build_part("mixer", spec.mixer, ctx)
+        self.feed_forward = self.ff_norm = None
+        if spec.feed_forward is not None:
+            self.ff_norm = build_part("norm", spec.norms["feed_forward"], ctx)
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, ctx)
+        self.scales = _LayerScales(extras.get("mixer_scale"),
+                                   extras.get("feed_forward_scale") if spec.feed_forward is not None else None,
+                                   int(spec.norms["mixer"].params["hidden_size"]))
+
+    @classmethod
+    def part_specs(cls, spec: LayerSpec):
+        extras = spec.extras or {}
+        out = [("norm", spec.norms["mixer"]), ("mixer", spec.mixer)]
+        if spec.feed_forward is not None:
+            out += [("norm", spec.norms["feed_forward"]), ("feed_forward", spec.feed_forward)]
+        names = {"mixer": extras.get("mixer_scale"),
+                 "feed_forward": extras.get("feed_forward_scale") if spec.feed_forward is not None else None}
+        out.append(("block", _scales_spec(names, int(spec.norms["mixer"].params["hidden_size"]))))
+        return out
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward, self.scales) if p is not None]
+
+    def cache_holders(self):
+        """The parts that keep something per request: the mixer, then what it names besides."""
+        return [self.mixer] + list(getattr(self.mixer, "state_holders", lambda: [])())
+
+    def _fused(self) -> bool:
+        """Whether both norms are the plain RMS norm with one eps: one kernel then writes both."""
+        return (type(self.mixer_norm) is RMSNorm and (self.ff_norm is None or (
+            type(self.ff_norm) is RMSNorm and self.ff_norm.eps == self.mixer_norm.eps)))
+
+    def forward(self, x: torch.Tensor, delta, batch):
+        tokens, hidden = x.shape
+        if self._fused() and (delta is None or isinstance(delta, ScaledPair)):
+            dtype, device = self.ctx.dtype, x.device
+            h1 = torch.empty((tokens, hidden), dtype=dtype, device=device)
+            h2 = torch.empty((tokens, hidden), dtype=dtype, device=device) if self.ff_norm is not None else None
+            d = delta or ScaledPair(None, None)
+            ops.pair_residual_norm(x, d.y1, d.s1, d.y2, d.s2, d.also, self.mixer_norm.weight_f32(),
+                                   self.ff_norm.weight_f32() if self.ff_norm is not None else None, h1, h2,
+                                   self.mixer_norm.eps)
+        else:
+            h1 = self.mixer_norm.forward(x, delta)
+            h2 = self.ff_norm.forward(x, None) if self.ff_norm is not None else None
+        y1 = self.mixer.forward(h1, batch)
+        y2 = self.feed_forward.forward(h2, batch) if self.feed_forward is not None else None
+        return x, ScaledPair(y1, self.scales.mixer, y2, self.scales.feed_forward)
+
+
+def _scales_spec(names: dict, hidden: int):
+    from .spec import PartSpec
+    return PartSpec("layer_scales", {"hidden_size": hidden}, dict(names))
+
+
+@register_part("block", "layer_scales")
+class _LayerScales:
+    """The per-channel scales of a parallel block's two outputs (fp32 [hidden] each), as a
+    part of its own so that the loader hears of the tensors. tensors: mixer, feed_forward
+    (either may be None)."""
+
+    def __init__(self, mixer_name, ff_name, hidden: int):
+        self.names = {"mixer": mixer_name, "feed_forward": ff_name}
+        self.hidden = hidden
+        self.mixer: torch.Tensor | None = None
+        self.feed_forward: torch.Tensor | None = None
+
+    @classmethod
+    def part_specs(cls, spec):
+        return []
+
+    @classmethod
+    def tensor_needs(cls, spec):
+        from .spec import TensorNeed
+        hidden = int(spec.params["hidden_size"])
+        return {name: TensorNeed((hidden,), role="vector") for name in spec.tensors.values() if name}
+
+    def load(self, tensors) -> None:
+        for role, name in self.names.items():
+            if name:
+                setattr(self, role, tensors[name].float().contiguous())

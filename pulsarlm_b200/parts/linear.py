@@ -86,7 +86,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if x.dtype == torch.bfloat16:
         k = x.shape[1]
         kernel = own_kernel_for(tokens, n, x.device, k)
-        if kernel is not None and x.stride(1) == 1 and weight.stride(1) == 1 and ops.gemm_bf16_supports(
+        if kernel is not None and x.stride(1) == 1 and weight.stride(1) == 1 and x.data_ptr() % 16 == 0 \
+                and weight.data_ptr() % 16 == 0 and ops.gemm_bf16_supports(
                 tokens, n, k, x.stride(0) if tokens > 1 else k, weight.stride(0) if n > 1 else k):
             out = torch.empty((tokens, n), dtype=out_dtype or torch.bfloat16, device=x.device)
             ops.gemm_bf16(x, weight, out, kernel=kernel)

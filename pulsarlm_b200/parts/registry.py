@@ -72,7 +72,8 @@ def _load_builtins() -> None:
     global _builtins_loaded
     if not _builtins_loaded:
         _builtins_loaded = True
-        from . import attention, basic, block, delta_rule, latent_attention, short_conv  # noqa: F401
+        from . import (attention, basic, block, delta_rule, diff_attention, gated_delta, latent_attention, moe,  # noqa: F401
+                       short_conv)
 
 
 def part_class(kind: str, name: str) -> type:

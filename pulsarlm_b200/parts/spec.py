@@ -42,7 +42,11 @@ class ModelSpec:
     """The whole model. `order` lists layer indices in the order they run; an
     index may appear twice (the layer then runs twice with the same weights and
     cache). A mixer whose params hold `cache_from = k` reads (and does not
-    write) the cache of layer k."""
+    write) the cache of layer k. `cache_per_run`: every entry of `order` keeps a
+    cache or state of its own (a layer that runs twice then has two, one per run),
+    and the cache manager is asked run by run instead of layer by layer.
+    `rejoin_runs`: places in `order` before which the embedding's output (the
+    stream as it entered the first layer) is added to the stream again."""
 
     hidden_size: int
     vocab_size: int
@@ -53,6 +57,8 @@ class ModelSpec:
     head: PartSpec
     eos_token_ids: tuple[int, ...] = ()
     max_position_embeddings: int | None = None
+    cache_per_run: bool = False
+    rejoin_runs: tuple[int, ...] = ()
 
 
 @dataclasses.dataclass(frozen=True)
