@@ -51,6 +51,8 @@ class BunosunLayer:
     rot_factor: float = 1.0
     # channel_delta
     taps: int | None = None
+    decay_rank: int | None = None      # inner sizes of the decay's and the gate's projections: None takes
+    gate_rank: int | None = None       # them from the stored tensors' shapes (random weights need them named)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -117,7 +119,9 @@ class BunosunConfig:
             else:
                 taps = read_field(mixer, "conv", int)
                 require_positive(f"{where}.mixer.conv", taps)
-                layers.append(BunosunLayer(kind, heads, kv_heads, dim, vdim, mlp, taps=taps))
+                layers.append(BunosunLayer(kind, heads, kv_heads, dim, vdim, mlp, taps=taps,
+                                           decay_rank=read_field(mixer, "decay_rank", int, None),
+                                           gate_rank=read_field(mixer, "gate_rank", int, None)))
         loop = text.get("loop") or {}
         start, stop = read_field(loop, "start", int, 0), read_field(loop, "stop", int, 0)
         times = read_field(loop, "times", int, 1)
@@ -151,6 +155,10 @@ class BunosunConfig:
                                     "scaling": {"factor": layer.rot_factor}}
             else:
                 mixer["conv"] = layer.taps
+                if layer.decay_rank is not None:
+                    mixer["decay_rank"] = layer.decay_rank
+                if layer.gate_rank is not None:
+                    mixer["gate_rank"] = layer.gate_rank
             mlp = None
             if layer.mlp is not None:
                 m = layer.mlp

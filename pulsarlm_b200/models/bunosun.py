@@ -38,7 +38,8 @@ def describe_bunosun(cfg: BunosunConfig) -> ModelSpec:
             mixer = PartSpec(
                 "channel_delta",
                 {"hidden_size": width, "n_heads": layer.heads, "qk_heads": layer.kv_heads, "head_dim": layer.dim,
-                 "value_dim": layer.vdim, "taps": layer.taps, "eps": cfg.norm_eps},
+                 "value_dim": layer.vdim, "taps": layer.taps, "eps": cfg.norm_eps, "decay_rank": layer.decay_rank,
+                 "gate_rank": layer.gate_rank},
                 {**{name: m + name for name in ("q", "k", "v", "b", "a1", "a2", "g1", "g2", "A_log", "dt_bias", "norm",
                                                  "o")},
                  "q_conv": m + "q.conv", "k_conv": m + "k.conv", "v_conv": m + "v.conv"})
