@@ -544,6 +544,33 @@ def rerilorn_config(width: int, layers: int, vocab: int = 32000) -> dict:
             "layers": [delta if i % 3 == 0 else latent for i in range(layers)]}
 
 
+def bunosun_config(width: int, runs: int, vocab: int = 32000) -> dict:
+    """A Bunosun model at a real model's layer sizes whose layers run `runs` times in all: a first
+    layer, then a looped pair (run twice), the rest after it. Every third run is a channel-wise
+    gated delta rule (heads of 64 x 64, four taps), the others differential attention (heads of two
+    maps of 64 over values of 128, four heads per kv head, window 1,024, half of each map rotated).
+    Feed-forward: 32 experts of width / 2 of which 4 are used, in 4 groups of which 2 stay, beside a
+    shared expert of width / 2 (2.5 x width active per token)."""
+    mlp = {"kind": "moe", "expert": {"ff": width // 2}, "shared": {"ff": width // 2},
+           "router": {"experts": 32, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    heads = max(1, width // 128)
+    attention = {"type": "attention", "mlp": mlp,
+                 "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "diff": 0.5,
+                           "scale": 0.125, "mask": {"size": 1024},
+                           "rot": {"base": 10000.0, "dims": 32, "scaling": {"factor": 4.0}}}}
+    delta = {"type": "channel_delta", "mlp": mlp,
+             "mixer": {"heads": width // 64, "kv_heads": width // 64, "dim": 64, "vdim": 64, "conv": 4,
+                       "decay_rank": 64, "gate_rank": 64}}
+    if runs >= 5:
+        layers = [attention, attention, delta] + [attention if i % 3 else delta for i in range(1, runs - 4)]
+        loop = {"start": 1, "stop": 3, "times": 2}
+    else:
+        layers = [attention, delta] + [attention] * (runs - 3)
+        loop = {"start": 0, "stop": 1, "times": 2}
+    return {"architecture": "Bunosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(width) ** 0.5}, "layers": layers, "loop": loop}
+
+
 def llama_config_like(width: int, layers: int, vocab: int = 32000) -> dict:
     """The Llama decoder at the same width, depth and vocabulary: heads of 64 in groups of
     four, gated feed-forward of 8/3 x width (the parameters of a plain one of 4 x width)."""
@@ -664,8 +691,130 @@ def design_kernels(width: int, pk: dict) -> dict:
     return out
 
 
+def bunosun_kernels(width: int, pk: dict) -> dict:
+    """The Bunosun design's kernels alone at one layer's sizes, each beside the like kernel of
+    the Llama or Rerilorn layer: milliseconds, algorithmic bytes or FLOPs, fraction of the copy
+    bandwidth."""
+    import torch
+
+    from pulsarlm_b200.kernels import ops
+    from pulsarlm_b200.parts import moe as moe_part
+    from pulsarlm_b200.parts.linear import gated_feed_forward
+    from pulsarlm_b200.parts.registry import BuildContext
+    from pulsarlm_b200.parts.spec import PartSpec
+
+    dev, bf = "cuda:0", torch.bfloat16
+    out: dict = {}
+
+    def note(name, ms, nbytes=None, flops=None):
+        out[name] = {"ms": ms}
+        if nbytes is not None:
+            out[name].update(bytes=nbytes, frac_of_hbm=nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"])
+        if flops is not None:
+            out[name].update(tflops=flops / (ms / 1e3) / 1e12, frac_of_bf16=flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"])
+
+    experts, top, ff = 32, 4, width // 2
+    spec = PartSpec("moe", {"hidden_size": width, "expert_size": ff, "n_experts": experts, "top": top, "groups": 4,
+                            "keep_groups": 2, "shared_size": None},
+                    {"router": "r", "correction": "c", "expert_gate": "e{e}.g", "expert_up": "e{e}.u",
+                     "expert_down": "e{e}.d"})
+    part = moe_part.RoutedExperts(spec, BuildContext(bf, torch.device(dev)))
+    tensors = {"r": torch.randn((experts, width), device=dev) * 0.02, "c": torch.zeros(experts, device=dev)}
+    for e in range(experts):
+        tensors[f"e{e}.g"] = (torch.randn((ff, width), device=dev) * 0.02).to(bf)
+        tensors[f"e{e}.u"] = (torch.randn((ff, width), device=dev) * 0.02).to(bf)
+        tensors[f"e{e}.d"] = (torch.randn((width, ff), device=dev) * 0.02).to(bf)
+    part.load(tensors)
+    del tensors
+    dense_ff = top * ff
+    dense_gate_up = (torch.randn((2 * dense_ff, width), device=dev) * 0.02).to(bf)
+    dense_down = (torch.randn((width, dense_ff), device=dev) * 0.02).to(bf)
+    for tokens, entries in ((2048, 1), (8, 8), (64, 64)):
+        tag = f"T{tokens}_E{entries}"
+        per = tokens // entries
+        entry = torch.arange(entries, dtype=torch.int32, device=dev).repeat_interleave(per)
+        slots = torch.arange(entries, dtype=torch.int32, device=dev)
+        first = torch.arange(0, tokens, per, dtype=torch.int32, device=dev)
+        count = torch.full((entries,), per, dtype=torch.int32, device=dev)
+        x = torch.randn((tokens, width), device=dev)
+        y = torch.randn((tokens, width), device=dev).to(bf)
+        h, h2 = torch.empty_like(y), torch.empty_like(y)
+        w32 = torch.ones(width, device=dev)
+        note(f"pair_residual_norm_{tag}", time_kernel(lambda: ops.pair_residual_norm(x, y, w32, y, w32, None, w32, w32,
+                                                                                     h, h2, 1e-6)),
+             tokens * width * (4 + 4 + 2 + 2 + 2 + 2))
+        note(f"add_rmsnorm_{tag} (Llama)", time_kernel(lambda: ops.add_rmsnorm(x, y, w32, 1e-6, h)),
+             tokens * width * (4 + 4 + 2 + 2))
+        # the routed feed-forward beside a dense gated one of the same active size
+        hb = torch.randn((tokens, width), device=dev).to(bf)
+        ids, _ = ops.moe_route(hb, part.router, part.correction, top, 4, 2)
+        used = int(torch.unique(ids).numel())
+        weight_bytes = used * 3 * ff * width * 2
+        note(f"routed_experts_{tag} ({used} experts used)", time_kernel(lambda: part.forward(hb, None)),
+             weight_bytes + tokens * width * 4, 2.0 * tokens * top * 3 * ff * width)
+        note(f"gated_feed_forward_{tag} (Llama, the same active size)",
+             time_kernel(lambda: gated_feed_forward(hb, dense_gate_up, dense_down)),
+             3 * dense_ff * width * 2 + tokens * width * 4, 2.0 * tokens * 3 * dense_ff * width)
+        note(f"moe_route_{tag}", time_kernel(lambda: ops.moe_route(hb, part.router, part.correction, top, 4, 2)),
+             tokens * width * 2 + experts * width * 4)
+        # the recurrence beside the generalized delta rule's (heads of 64 x 64 both)
+        heads = width // 64
+        qkv = torch.randn((tokens, 3 * width), device=dev).to(bf)
+        b_pre = torch.randn((tokens, heads), device=dev).to(bf)
+        a_pre = torch.randn((tokens, width), device=dev).to(bf)
+        g_pre = torch.randn((tokens, width), device=dev).to(bf)
+        S = torch.zeros((entries + 1, heads, 64, 64), device=dev)
+        o = torch.empty((tokens, width), dtype=bf, device=dev)
+        a_log = torch.zeros(heads, device=dev)
+        note(f"gated_delta_{tag}",
+             time_kernel(lambda: ops.gated_delta(qkv[:, :width], qkv[:, width:2 * width], qkv[:, 2 * width:], b_pre, a_pre,
+                                                 g_pre, a_log, w32, torch.ones(64, device=dev), S, first, count, slots, o,
+                                                 heads, heads, 64, 64, 1e-6, 0.125, 1e-6)),
+             tokens * width * 2 * 6 + entries * heads * 64 * 64 * 4 * 2)
+        proj = torch.randn((tokens, 5 * width + 64), device=dev).to(bf)
+        parts = [proj[:, i * width:(i + 1) * width] for i in range(5)]
+        note(f"delta_rule_{tag} (Rerilorn)",
+             time_kernel(lambda: ops.delta_rule(*parts, a_pre, w32, w32, w32, S, first, count, slots, o, heads, 64,
+                                                0.6065, 1e-6, 1e-6)),
+             tokens * width * 2 * 7 + entries * heads * 64 * 64 * 4 * 2)
+        state = torch.zeros((entries + 1, 3, 3 * width), dtype=bf, device=dev)
+        cw = torch.randn((3 * width, 4), device=dev)
+        filtered = torch.empty((tokens, 3 * width), dtype=bf, device=dev)
+
+        def conv():
+            ops.short_conv_act(qkv, cw, state, entry, slots, filtered, residual=False, act="silu")
+            ops.short_conv_state_strided(qkv, entry, slots, state)
+        note(f"short_conv_silu_{tag} (3 x width channels)", time_kernel(conv), tokens * 3 * width * 4 + entries * 9 * width * 4)
+        # the maps' layout, rotation and cache write beside the Llama layer's rotation and write
+        n_heads, n_kv, page = width // 128, max(1, width // 512), 16
+        n_pages = tokens // page + entries + 1
+        pools = torch.zeros((2, n_pages, n_kv, page, 128), dtype=bf, device=dev)
+        table = torch.arange(entries * (per // page + 1), dtype=torch.int32, device=dev).view(entries, -1)
+        pos = torch.arange(per, dtype=torch.int32, device=dev).repeat(entries)
+        mixed = torch.randn((tokens, (n_heads + 2 * n_kv) * 128), device=dev).to(bf)
+        q_end, k_end = n_heads * 128, (n_heads + n_kv) * 128
+        q_out = torch.empty((tokens, 2 * n_heads, 128), dtype=bf, device=dev)
+        inv = torch.rand(16, dtype=torch.float64, device=dev)
+        note(f"rope_maps_write_{tag}",
+             time_kernel(lambda: ops.rope_maps_write(mixed[:, :q_end], mixed[:, q_end:k_end], mixed[:, k_end:], pos, entry,
+                                                     table, pools[0], pools[1], page, inv, 32, n_heads, n_kv, 2, 64, 128,
+                                                     q_out, None)),
+             tokens * (n_heads * 128 * 2 * 3 + n_kv * 128 * 2 * 4))
+        inv64 = torch.rand(64, dtype=torch.float64, device=dev)
+        note(f"rope_kv_write_{tag} (Llama)",
+             time_kernel(lambda: ops.rope_kv_write(mixed[:, :q_end].view(tokens, n_heads, 128),
+                                                   mixed[:, q_end:k_end].view(tokens, n_kv, 128),
+                                                   mixed[:, k_end:].view(tokens, n_kv, 128), pos, entry, table, pools[0],
+                                                   pools[1], page, inv64, 128, None)),
+             tokens * (n_heads * 128 * 2 * 2 + n_kv * 128 * 2 * 4))
+        combined = torch.empty((tokens, n_heads * 128), dtype=bf, device=dev)
+        note(f"diff_combine_{tag}", time_kernel(lambda: ops.diff_combine(q_out, combined, n_heads, 128, 0.4, 1e-6, 0.5)),
+             tokens * n_heads * 128 * 2 * 3)
+    return out
+
+
 def run_design(args) -> dict:
-    """Prefill and decode throughput of the Rerilorn design at a few sizes beside the Llama
+    """Prefill and decode throughput of the named design at a few sizes beside the Llama
     decoder at the same width, depth and vocabulary (random weights), and the design's own
     kernels alone."""
     import gc
@@ -680,7 +829,8 @@ def run_design(args) -> dict:
     prompt, batch, context = 2048, 8, 2048
     with ClockSampler() as clocks:
         for width, layers in ((1024, 6), (2048, 6), (4096, 3)):
-            for name, cfg in (("rerilorn", rerilorn_config(width, layers)), ("llama", llama_config_like(width, layers))):
+            mine = bunosun_config(width, layers) if args.design == "bunosun" else rerilorn_config(width, layers)
+            for name, cfg in ((args.design, mine), ("llama", llama_config_like(width, layers))):
                 vocab = cfg.get("vocab", cfg.get("vocab_size"))
                 n_pages = (batch * (context + 256) + 4 * prompt) // PAGE_SIZE
                 engine = Engine(cfg, dtype="bfloat16", device="cuda:0", n_pages=n_pages, page_size=PAGE_SIZE,
@@ -711,10 +861,11 @@ def run_design(args) -> dict:
                 del engine
                 gc.collect()
                 torch.cuda.empty_cache()
-        kernels = design_kernels(2048, pk)
+        kernels = bunosun_kernels(2048, pk) if args.design == "bunosun" else design_kernels(2048, pk)
     summary = clocks.summary()
-    return {"metric": "prefill and decode tok/s of the Rerilorn design beside the Llama decoder at equal sizes",
-            "design": "rerilorn", "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+    return {"metric": f"prefill and decode tok/s of the {args.design.capitalize()} design beside the Llama decoder at "
+                      f"equal sizes",
+            "design": args.design, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "dtype": "bf16", "data": "synthetic: random weights drawn on the device, uniform random token ids",
             "config": {"prompt": prompt, "decode_batch": batch, "decode_context": context, "page_size": PAGE_SIZE,
                        "peaks": pk["source"], "l2": "kernels alone: a 256 MB buffer is rewritten between calls"},
@@ -724,9 +875,9 @@ def run_design(args) -> dict:
 
 def main() -> int:
     p = argparse.ArgumentParser()
-    p.add_argument("--design", default="llama", choices=["llama", "rerilorn"],
-                   help="llama: the headline workload (the default); rerilorn: that design's prefill and decode "
-                        "throughput at a few sizes beside the Llama decoder at equal sizes, and its kernels alone")
+    p.add_argument("--design", default="llama", choices=["llama", "rerilorn", "bunosun"],
+                   help="llama: the headline workload (the default); rerilorn, bunosun: that design's prefill and "
+                        "decode throughput at a few sizes beside the Llama decoder at equal sizes, and its kernels alone")
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=128)
     p.add_argument("--warmup", type=int, default=8)
@@ -748,7 +899,7 @@ def main() -> int:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     args.warmup = max(3, args.warmup)
-    if args.design == "rerilorn":
+    if args.design in ("rerilorn", "bunosun"):
         args.steps = min(args.steps, 64)
         print(json.dumps(run_design(args)))
         return 0

@@ -13,8 +13,9 @@
 // The scan: a CTA per (batch entry, head, block of value columns) walks the entry's rows in
 // order. A column of S never meets another column, so each column lives in registers:
 // `parts` neighbouring lanes share a column and each holds every parts-th of its rows. The
-// rows are taken in chunks: all threads turn a chunk's projections into the fp32 vectors
-// q^, k^, g and the scalar b in shared memory (the unit factors by a warp per token, the
+// rows are taken in chunks: while one chunk is worked on, the next chunk's projections
+// arrive in shared memory (cp.async); all threads turn a chunk's projections into the fp32
+// vectors q^, k^, g and the scalar b (the unit factors by a warp per token, the
 // exponentials one (token, channel) per thread), then the tokens update the state one after
 // the other with nothing but the shuffles among a column's lanes between them. The raw o
 // goes to scratch in fp32; a second kernel norms it per head, applies the norm's weight and
@@ -22,6 +23,8 @@
 // result depends on the tokens before it only: not on how the prompt was cut, on the chunks
 // or on the rest of the batch.
 #include "common.cuh"
+
+#include "mma_helpers.cuh"
 
 namespace {
 
@@ -45,24 +48,72 @@ struct GatedDeltaParams {
     const int32_t* slots;
     float* o_raw;
     int n_heads, qk_heads, dim, vdim, parts, cols, chunk;
+    int async_loads;  // every row of every operand starts on 16 bytes
     float unit_eps, q_scale;
 };
 
 __device__ __forceinline__ float softplus_f32(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 
+// One chunk's projections -> shared memory: [token][q, k, a~][dim], then [token][cols] of v.
+template <typename scalar_t>
+__device__ __forceinline__ void load_chunk(const GatedDeltaParams& p, scalar_t* raw, const scalar_t* q,
+                                           const scalar_t* k, const scalar_t* a_pre, const scalar_t* v, int64_t t0,
+                                           int n, int n_cols) {
+    const int dim = p.dim;
+    scalar_t* raw_v = raw + p.chunk * 3 * dim;
+    if (p.async_loads) {
+        constexpr int kPer = 16 / sizeof(scalar_t);
+        const int gv = dim / kPer, gc = p.cols / kPer;
+        const int per_token = 3 * gv + gc;
+        for (int idx = threadIdx.x; idx < n * per_token; idx += blockDim.x) {
+            const int c = idx / per_token, g = idx % per_token;
+            if (g < 3 * gv) {
+                const int which = g / gv, e = (g % gv) * kPer;
+                const scalar_t* src = which == 0 ? q + (t0 + c) * p.qkv_stride
+                                    : which == 1 ? k + (t0 + c) * p.qkv_stride : a_pre + (t0 + c) * p.a_stride;
+                cp_async_16(raw + (c * 3 + which) * dim + e, src + e);
+            } else {
+                const int e = (g - 3 * gv) * kPer;
+                if (e < n_cols) {  // (n_cols is a multiple of kPer here)
+                    cp_async_16(raw_v + c * p.cols + e, v + (t0 + c) * p.qkv_stride + e);
+                }
+            }
+        }
+    } else {
+        const int per_token = 3 * dim + n_cols;
+        for (int idx = threadIdx.x; idx < n * per_token; idx += blockDim.x) {
+            const int c = idx / per_token, g = idx % per_token;
+            if (g < 3 * dim) {
+                const int which = g / dim, e = g % dim;
+                const scalar_t* src = which == 0 ? q + (t0 + c) * p.qkv_stride
+                                    : which == 1 ? k + (t0 + c) * p.qkv_stride : a_pre + (t0 + c) * p.a_stride;
+                raw[(c * 3 + which) * dim + e] = src[e];
+            } else {
+                const int e = g - 3 * dim;
+                raw_v[c * p.cols + e] = v[(t0 + c) * p.qkv_stride + e];
+            }
+        }
+    }
+    cp_async_commit();
+}
+
 template <typename scalar_t>
 __global__ void __launch_bounds__(512) gated_delta_scan_kernel(const GatedDeltaParams p) {
     pl_grid_trigger();
     pl_grid_wait();
-    extern __shared__ float shared[];
+    extern __shared__ __align__(16) unsigned char smem[];
     const int dim = p.dim, parts = p.parts, chunk = p.chunk, cols = p.cols;
-    float* sq = shared;                 // [chunk][dim]
+    float* sq = reinterpret_cast<float*>(smem);  // [chunk][dim]
     float* sk = sq + chunk * dim;       // [chunk][dim]
     float* sg = sk + chunk * dim;       // [chunk][dim]
-    float* sv = sg + chunk * dim;       // [chunk][cols]
-    float* sb = sv + chunk * cols;      // [chunk]
+    float* sb = sg + chunk * dim;       // [chunk]
     float* inv_q = sb + chunk;          // [chunk]
     float* inv_k = inv_q + chunk;       // [chunk]
+    float* bias = sq + (chunk * (3 * dim + 3) + 3) / 4 * 4;  // [dim], on 16 bytes like the buffers after it
+    // then two buffers of a chunk's projections as they arrive
+    const int raw_elems = chunk * (3 * dim + cols);
+    const int raw_bytes = (raw_elems * static_cast<int>(sizeof(scalar_t)) + 15) / 16 * 16;
+    unsigned char* raw_base = reinterpret_cast<unsigned char*>(bias + ((dim + 3) / 4) * 4);
 
     const int e = blockIdx.x, head = blockIdx.y;
     const int qk_head = head / (p.n_heads / p.qk_heads);
@@ -78,9 +129,12 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(const GatedDeltaP
     const scalar_t* a_pre = static_cast<const scalar_t*>(p.a_pre) + static_cast<int64_t>(head) * dim;
     const scalar_t* b_pre = static_cast<const scalar_t*>(p.b_pre) + head;
     const float rate = expf(p.a_log[head]);
-    const float* bias = p.dt_bias + static_cast<int64_t>(head) * dim;
     float* mine = p.state + ((static_cast<int64_t>(p.slots[e]) * p.n_heads + head) * dim) * p.vdim + col0;
 
+    load_chunk<scalar_t>(p, reinterpret_cast<scalar_t*>(raw_base), q, k, a_pre, v, first, min(chunk, count), n_cols);
+    for (int i = tid; i < dim; i += blockDim.x) {
+        bias[i] = p.dt_bias[static_cast<int64_t>(head) * dim + i];
+    }
     float S[kRows];
 #pragma unroll
     for (int m = 0; m < kRows; ++m) {
@@ -88,65 +142,89 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(const GatedDeltaP
         S[m] = active && i < dim ? mine[static_cast<int64_t>(i) * p.vdim + col] : 0.0f;
     }
 
-    for (int done = 0; done < count; done += chunk) {
+    int buffer = 0;
+    for (int done = 0; done < count; done += chunk, buffer ^= 1) {
         const int n = min(chunk, count - done);
         const int64_t t0 = first + done;
-        __syncthreads();  // (the chunk before has been read)
+        const scalar_t* raw = reinterpret_cast<const scalar_t*>(raw_base + buffer * raw_bytes);
+        // The next chunk sets out now (its buffer was last read two chunks ago); this one must have landed.
+        __syncthreads();
+        if (done + chunk < count) {
+            load_chunk<scalar_t>(p, reinterpret_cast<scalar_t*>(raw_base + (buffer ^ 1) * raw_bytes), q, k, a_pre, v,
+                                 t0 + chunk, min(chunk, count - done - chunk), n_cols);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
         for (int c = warp; c < n; c += warps) {
-            const scalar_t* qr = q + (t0 + c) * p.qkv_stride;
-            const scalar_t* kr = k + (t0 + c) * p.qkv_stride;
+            float b = 0.0f;
+            if (lane == 0) {
+                b = pl_load(b_pre + (t0 + c) * p.b_stride);
+            }
+            const scalar_t* qr = raw + (c * 3) * dim;
+            const scalar_t* kr = qr + dim;
             float qq = 0.0f, kk = 0.0f;
             for (int i = lane; i < dim; i += 32) {
-                const float a = pl_load(qr + i), b = pl_load(kr + i);
-                qq = fmaf(a, a, qq);
-                kk = fmaf(b, b, kk);
+                const float x = pl_load(qr + i), y = pl_load(kr + i);
+                qq = fmaf(x, x, qq);
+                kk = fmaf(y, y, kk);
             }
             qq = pl_warp_sum(qq);
             kk = pl_warp_sum(kk);
             if (lane == 0) {
                 inv_q[c] = p.q_scale / sqrtf(qq + p.unit_eps);
                 inv_k[c] = 1.0f / sqrtf(kk + p.unit_eps);
-                sb[c] = 1.0f / (1.0f + expf(-pl_load(b_pre + (t0 + c) * p.b_stride)));
+                sb[c] = 1.0f / (1.0f + expf(-b));
             }
         }
         __syncthreads();
         for (int idx = tid; idx < n * dim; idx += blockDim.x) {
             const int c = idx / dim, i = idx - c * dim;
-            sq[idx] = pl_load(q + (t0 + c) * p.qkv_stride + i) * inv_q[c];
-            sk[idx] = pl_load(k + (t0 + c) * p.qkv_stride + i) * inv_k[c];
-            sg[idx] = expf(-rate * softplus_f32(pl_load(a_pre + (t0 + c) * p.a_stride + i) + bias[i]));
-        }
-        for (int idx = tid; idx < n * cols; idx += blockDim.x) {
-            const int c = idx / cols, j = idx - c * cols;
-            sv[idx] = j < n_cols ? pl_load(v + (t0 + c) * p.qkv_stride + j) : 0.0f;
+            const scalar_t* token = raw + c * 3 * dim;
+            sq[idx] = pl_load(token + i) * inv_q[c];
+            sk[idx] = pl_load(token + dim + i) * inv_k[c];
+            sg[idx] = expf(-rate * softplus_f32(pl_load(token + 2 * dim + i) + bias[i]));
         }
         __syncthreads();
+        const scalar_t* raw_v = raw + chunk * 3 * dim;
         for (int c = 0; c < n; ++c) {
             const float* kq = sq + c * dim;
             const float* kk = sk + c * dim;
             const float* kg = sg + c * dim;
-            float dot = 0.0f;
+            const float vj = active ? pl_load(raw_v + c * cols + col) : 0.0f;
+            float dot0 = 0.0f, dot1 = 0.0f;
 #pragma unroll
-            for (int m = 0; m < kRows; ++m) {
-                const int i = part + m * parts;
+            for (int m = 0; m < kRows; m += 2) {
+                const int i = part + m * parts, i2 = i + parts;
                 if (i < dim) {
                     S[m] *= kg[i];
-                    dot = fmaf(S[m], kk[i], dot);
+                    dot0 = fmaf(S[m], kk[i], dot0);
+                }
+                if (i2 < dim) {
+                    S[m + 1] *= kg[i2];
+                    dot1 = fmaf(S[m + 1], kk[i2], dot1);
                 }
             }
+            float dot = dot0 + dot1;
             for (int offset = parts >> 1; offset > 0; offset >>= 1) {
                 dot += __shfl_xor_sync(0xffffffffu, dot, offset);
             }
-            const float u = sb[c] * ((active ? sv[c * cols + col] : 0.0f) - dot);
-            float o = 0.0f;
+            const float u = sb[c] * (vj - dot);
+            float o0 = 0.0f, o1 = 0.0f;
 #pragma unroll
-            for (int m = 0; m < kRows; ++m) {
-                const int i = part + m * parts;
+            for (int m = 0; m < kRows; m += 2) {
+                const int i = part + m * parts, i2 = i + parts;
                 if (i < dim) {
                     S[m] = fmaf(kk[i], u, S[m]);
-                    o = fmaf(S[m], kq[i], o);
+                    o0 = fmaf(S[m], kq[i], o0);
+                }
+                if (i2 < dim) {
+                    S[m + 1] = fmaf(kk[i2], u, S[m + 1]);
+                    o1 = fmaf(S[m + 1], kq[i2], o1);
                 }
             }
+            float o = o0 + o1;
             for (int offset = parts >> 1; offset > 0; offset >>= 1) {
                 o += __shfl_xor_sync(0xffffffffu, o, offset);
             }
@@ -224,19 +302,35 @@ PL_API int pl_gated_delta(const void* q, const void* k, const void* v, int64_t q
         cols = vdim;
     }
     int threads = ((cols * parts + 31) / 32) * 32;
+    const size_t elem = dtype == PL_F32 ? 4 : 2;
+    auto bytes_for = [&](int chunk) {
+        const size_t vectors = ((static_cast<size_t>(chunk) * (3 * dim + 3) + 3) / 4 * 4 + (dim + 3) / 4 * 4) * sizeof(float);
+        const size_t raw = (static_cast<size_t>(chunk) * (3 * dim + cols) * elem + 15) / 16 * 16;
+        return vectors + 2 * raw;
+    };
     int chunk = kChunkMost;
-    while (chunk > 1 && static_cast<size_t>(chunk) * (3 * dim + cols + 3) * sizeof(float) > 40 * 1024) {
+    while (chunk > 1 && bytes_for(chunk) > 44 * 1024) {
         chunk /= 2;
     }
-    const size_t smem = static_cast<size_t>(chunk) * (3 * dim + cols + 3) * sizeof(float);
+    const size_t smem = bytes_for(chunk);
+    PL_REQUIRE(smem <= 200 * 1024, "gated_delta: key size %d needs too much shared memory", dim);
+    const int per = static_cast<int>(16 / elem);
+    const int async_loads = dim % per == 0 && cols % per == 0 && vdim % per == 0 && qkv_stride % per == 0 &&
+        a_stride % per == 0 &&
+        ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+          reinterpret_cast<uintptr_t>(a_pre)) & 15) == 0;
     GatedDeltaParams p;
     p.q = q; p.k = k; p.v = v; p.qkv_stride = qkv_stride; p.b_pre = b_pre; p.b_stride = b_stride; p.a_pre = a_pre;
     p.a_stride = a_stride; p.a_log = a_log; p.dt_bias = dt_bias; p.state = state; p.first_rows = first_rows;
     p.counts = counts; p.slots = slots; p.o_raw = o_raw; p.n_heads = n_heads; p.qk_heads = qk_heads; p.dim = dim;
-    p.vdim = vdim; p.parts = parts; p.cols = cols; p.chunk = chunk; p.unit_eps = unit_eps; p.q_scale = q_scale;
+    p.vdim = vdim; p.parts = parts; p.cols = cols; p.chunk = chunk; p.async_loads = async_loads; p.unit_eps = unit_eps; p.q_scale = q_scale;
     const dim3 grid(n_entries, n_heads, (vdim + cols - 1) / cols);
     const int n_pairs = n_tokens * n_heads;
     PL_DISPATCH_DTYPE(dtype, "gated_delta", {
+        if (smem > 48 * 1024) {
+            cudaFuncSetAttribute(gated_delta_scan_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+        }
         pl_launch_overlapped(gated_delta_scan_kernel<scalar_t>, grid, dim3(threads), smem, stream, p);
         pl_launch_overlapped(gated_delta_finish_kernel<scalar_t>, dim3((n_pairs + 3) / 4), dim3(128), 0, stream,
                              static_cast<const float*>(o_raw), norm, static_cast<const scalar_t*>(gate_pre), gate_stride,

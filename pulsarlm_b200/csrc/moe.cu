@@ -58,11 +58,26 @@ __global__ void moe_route_kernel(const scalar_t* __restrict__ h, int64_t h_strid
         row[i] = pl_load(h + t * h_stride + i);
     }
     __syncthreads();
+    const bool vectors = (hidden & 3) == 0 && (reinterpret_cast<uintptr_t>(router) & 15) == 0;
     for (int e = warp; e < n_experts; e += warps) {
         const float* w = router + static_cast<int64_t>(e) * hidden;
         float z = 0.0f;
-        for (int i = lane; i < hidden; i += 32) {
-            z = fmaf(row[i], w[i], z);
+        if (vectors) {
+            // (the same products in the same order per lane as the loop below would make with a stride of 4 lanes'
+            // worth: what matters is that the order depends on the width alone)
+#pragma unroll 4
+            for (int i = lane * 4; i < hidden; i += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + i);
+                const float4 xv = *reinterpret_cast<const float4*>(row + i);
+                z = fmaf(xv.x, wv.x, z);
+                z = fmaf(xv.y, wv.y, z);
+                z = fmaf(xv.z, wv.z, z);
+                z = fmaf(xv.w, wv.w, z);
+            }
+        } else {
+            for (int i = lane; i < hidden; i += 32) {
+                z = fmaf(row[i], w[i], z);
+            }
         }
         z = pl_warp_sum(z);
         if (lane == 0) {
@@ -203,6 +218,46 @@ __device__ __forceinline__ float warp_dot(const scalar_t* __restrict__ w, const 
     return pl_warp_sum(sum);
 }
 
+// ROWS dot products at once, rows `row_stride` elements apart from `w`: every lane first asks for
+// all the rows' vectors of its place, then multiplies, so that ROWS loads are in flight per lane.
+template <typename scalar_t, int ROWS>
+__device__ __forceinline__ void warp_dots(const scalar_t* __restrict__ w, int64_t row_stride,
+                                          const float* __restrict__ x, int n, bool vectors, int lane,
+                                          float (&sums)[ROWS]) {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        sums[r] = 0.0f;
+    }
+    if (vectors) {
+        constexpr int kCount = Vec<scalar_t>::kCount;
+        for (int i = lane * kCount; i < n; i += 32 * kCount) {
+            float wv[ROWS][kCount];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                Vec<scalar_t>::load(w + r * row_stride + i, wv[r]);
+            }
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+                for (int j = 0; j < kCount; ++j) {
+                    sums[r] = fmaf(wv[r][j], x[i + j], sums[r]);
+                }
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                sums[r] = fmaf(pl_load(w + r * row_stride + i), x[i], sums[r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        sums[r] = pl_warp_sum(sums[r]);
+    }
+}
+
 constexpr int kFeaturesPerWarp = 4;
 
 // Block (pair, feature block): act[pair, f] = silu(gate_e[f] . h) * (up_e[f] . h).
@@ -227,6 +282,24 @@ __global__ void moe_gate_up_kernel(const scalar_t* __restrict__ h, int64_t h_str
     }
     const scalar_t* weights = gate_up + static_cast<int64_t>(e) * 2 * ff * hidden;  // [gate rows; up rows]
     const int f0 = (blockIdx.y * warps + warp) * kFeaturesPerWarp;
+    if (f0 + kFeaturesPerWarp <= ff) {
+        // The warp's four gate rows are neighbours, and so are its up rows: eight loads in flight per lane.
+        float g[kFeaturesPerWarp], u[kFeaturesPerWarp];
+        warp_dots<scalar_t, kFeaturesPerWarp>(weights + static_cast<int64_t>(f0) * hidden, hidden, row, hidden, vectors,
+                                              lane, g);
+        warp_dots<scalar_t, kFeaturesPerWarp>(weights + static_cast<int64_t>(ff + f0) * hidden, hidden, row, hidden,
+                                              vectors, lane, u);
+        if (lane < kFeaturesPerWarp) {
+            float gl = g[0], ul = u[0];
+#pragma unroll
+            for (int r = 1; r < kFeaturesPerWarp; ++r) {
+                gl = lane == r ? g[r] : gl;
+                ul = lane == r ? u[r] : ul;
+            }
+            pl_store(act + static_cast<int64_t>(pair) * ff + f0 + lane, silu_f32(gl) * ul);
+        }
+        return;
+    }
     for (int f = f0; f < min(f0 + kFeaturesPerWarp, ff); ++f) {
         const float g = warp_dot<scalar_t>(weights + static_cast<int64_t>(f) * hidden, row, hidden, vectors, lane);
         const float u = warp_dot<scalar_t>(weights + static_cast<int64_t>(ff + f) * hidden, row, hidden, vectors, lane);
@@ -254,6 +327,40 @@ __global__ void moe_down_kernel(const scalar_t* __restrict__ act, const scalar_t
     }
     __syncthreads();
     const int c0 = (blockIdx.y * warps + warp) * kChannelsPerWarp;
+    if (c0 + kChannelsPerWarp <= hidden) {
+        float sums[kChannelsPerWarp];
+#pragma unroll
+        for (int r = 0; r < kChannelsPerWarp; ++r) {
+            sums[r] = 0.0f;
+        }
+        for (int j = 0; j < top; ++j) {
+            const int e = ids[static_cast<int64_t>(t) * top + j];
+            if (e < 0 || e >= n_experts) {
+                continue;
+            }
+            float dots[kChannelsPerWarp];
+            warp_dots<scalar_t, kChannelsPerWarp>(down + (static_cast<int64_t>(e) * hidden + c0) * ff, ff, rows + j * ff, ff,
+                                                  vectors, lane, dots);
+            const float weight = weights[static_cast<int64_t>(t) * top + j];
+#pragma unroll
+            for (int r = 0; r < kChannelsPerWarp; ++r) {
+                sums[r] = fmaf(weight, dots[r], sums[r]);
+            }
+        }
+        if (lane < kChannelsPerWarp) {
+            float sum = sums[0];
+#pragma unroll
+            for (int r = 1; r < kChannelsPerWarp; ++r) {
+                sum = lane == r ? sums[r] : sum;
+            }
+            const int c = c0 + lane;
+            if (also != nullptr) {
+                sum += pl_load(also + static_cast<int64_t>(t) * hidden + c);
+            }
+            pl_store(out + static_cast<int64_t>(t) * hidden + c, sum);
+        }
+        return;
+    }
     for (int c = c0; c < min(c0 + kChannelsPerWarp, hidden); ++c) {
         float sum = 0.0f;
         for (int j = 0; j < top; ++j) {
@@ -368,7 +475,7 @@ PL_API int pl_moe_route(const void* h, int64_t h_stride, const float* router, co
             cudaFuncSetAttribute(moe_route_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem));
         }
-        pl_launch_overlapped(moe_route_kernel<scalar_t>, dim3(n_tokens), dim3(256), smem, stream,
+        pl_launch_overlapped(moe_route_kernel<scalar_t>, dim3(n_tokens), dim3(n_experts > 8 ? 512 : 256), smem, stream,
                              static_cast<const scalar_t*>(h), h_stride, router, correction, ids, weights, hidden,
                              n_experts, top, n_groups, keep);
     });

@@ -38,8 +38,8 @@ __global__ void rope_maps_write_kernel(const scalar_t* __restrict__ q, const sca
                                        scalar_t* __restrict__ k_pool, scalar_t* __restrict__ v_pool,
                                        int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                                        const double* __restrict__ inv_freq, int rotary, int n_heads, int n_kv_heads,
-                                       int maps, int dim, int vdim, int padded, scalar_t* __restrict__ q_out,
-                                       int32_t* status) {
+                                       int maps, int dim, int vdim, int padded, int rows_per_block,
+                                       scalar_t* __restrict__ q_out, int32_t* status) {
     extern __shared__ float sincos[];  // [rotary/2] cos, [rotary/2] sin
     pl_grid_trigger();
     const int t = blockIdx.x;
@@ -59,10 +59,13 @@ __global__ void rope_maps_write_kernel(const scalar_t* __restrict__ q, const sca
     }
     pl_grid_wait();
     __syncthreads();
+    // Block (t, y) takes `rows_per_block` rows from y * rows_per_block, where rows 0 .. q_rows - 1 are the
+    // query rows and the next n_kv_heads the key/value rows: a step of few tokens spreads over many blocks.
     const int q_rows = n_heads * maps;
+    const int row0 = blockIdx.y * rows_per_block, row1 = min(row0 + rows_per_block, q_rows + n_kv_heads);
     const scalar_t* qt = q + t * row_stride;
     scalar_t* qo = q_out + static_cast<int64_t>(t) * q_rows * padded;
-    for (int idx = threadIdx.x; idx < q_rows * padded; idx += blockDim.x) {
+    for (int idx = row0 * padded + threadIdx.x; idx < min(row1, q_rows) * padded; idx += blockDim.x) {
         const int hm = idx / padded, d = idx % padded;
         const int m = hm % maps;
         const int e = d - m * dim;
@@ -72,12 +75,13 @@ __global__ void rope_maps_write_kernel(const scalar_t* __restrict__ q, const sca
         }
         pl_store(qo + idx, value);
     }
-    if (page < 0) {
+    if (page < 0 || row1 <= q_rows) {
         return;
     }
     const scalar_t* kt = k + t * row_stride;
     const scalar_t* vt = v + t * row_stride;
-    for (int idx = threadIdx.x; idx < n_kv_heads * padded; idx += blockDim.x) {
+    for (int idx = (max(row0, q_rows) - q_rows) * padded + threadIdx.x; idx < (row1 - q_rows) * padded;
+         idx += blockDim.x) {
         const int g = idx / padded, d = idx % padded;
         const int64_t at = page * page_stride + g * head_stride + static_cast<int64_t>(p % page_size) * padded + d;
         float key = 0.0f;
@@ -141,16 +145,18 @@ PL_API int pl_rope_maps_write(const void* q, const void* k, const void* v, int64
     if (n_tokens == 0) {
         return 0;
     }
-    const int work = n_heads * maps * padded;
-    const int threads = work >= 1024 ? 256 : 128;
+    const int all_rows = n_heads * maps + n_kv_heads;
+    const int rows_per_block = n_tokens >= 256 ? all_rows : 4;
+    const int threads = rows_per_block * padded >= 1024 ? 256 : 128;
     PL_DISPATCH_DTYPE(dtype, "rope_maps_write", {
-        pl_launch_overlapped(rope_maps_write_kernel<scalar_t>, dim3(n_tokens), dim3(threads),
+        pl_launch_overlapped(rope_maps_write_kernel<scalar_t>, dim3(n_tokens, (all_rows + rows_per_block - 1) / rows_per_block),
+                             dim3(threads),
                              static_cast<size_t>(rotary > 0 ? rotary : 1) * sizeof(float), stream,
                              static_cast<const scalar_t*>(q), static_cast<const scalar_t*>(k),
                              static_cast<const scalar_t*>(v), row_stride, pos, entry, table, table_width,
                              static_cast<scalar_t*>(k_pool), static_cast<scalar_t*>(v_pool), page_stride, head_stride,
                              page_size, n_pages, inv_freq, rotary, n_heads, n_kv_heads, maps, dim, vdim, padded,
-                             static_cast<scalar_t*>(q_out), status);
+                             rows_per_block, static_cast<scalar_t*>(q_out), status);
     });
     PL_CHECK_LAUNCH("rope_maps_write");
     return 0;

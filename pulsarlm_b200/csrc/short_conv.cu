@@ -227,7 +227,8 @@ static int short_conv_launch(const void* h, int64_t h_stride, const float* weigh
     }
     const int vectors = width % 4 == 0 && h_stride % 4 == 0 &&
         ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-    if (vectors && taps >= 2 && taps <= 6) {
+    // (few rows: steps of single tokens, where a block per row is ahead of a block walking rows one after the other)
+    if (vectors && taps >= 2 && taps <= 6 && n_tokens > 64) {
         const dim3 grid((n_tokens + kRowsPerBlock - 1) / kRowsPerBlock, (width / 4 + 127) / 128);
 #define PL_CONV_ROWS(T)                                                                                          \
     pl_launch_overlapped(short_conv_rows_kernel<scalar_t, T>, grid, dim3(128), 0, stream,                        \
