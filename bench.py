@@ -782,6 +782,8 @@ def bunosun_kernels(width: int, pk: dict) -> dict:
         filtered = torch.empty((tokens, 3 * width), dtype=bf, device=dev)
 
         def conv():
+            if per == 1 and ops.short_conv_single(qkv, cw, state, entry, slots, filtered, residual=False, act="silu"):
+                return
             ops.short_conv_act(qkv, cw, state, entry, slots, filtered, residual=False, act="silu")
             ops.short_conv_state_strided(qkv, entry, slots, state)
         note(f"short_conv_silu_{tag} (3 x width channels)", time_kernel(conv), tokens * 3 * width * 4 + entries * 9 * width * 4)

@@ -243,6 +243,171 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(const GatedDeltaP
     }
 }
 
+// The same scan with the key size and the lanes per column known to the compiler: a lane holds
+// DIM / PARTS = 16 consecutive rows of its column, reads its share of q^, k^ and g with 16-byte
+// loads, and fetches them one token ahead of the token whose chain it is in. (A lane's rows
+// differ from the kernel above, so the sums' order does; which kernel runs depends on the
+// sizes alone.)
+template <typename scalar_t, int DIM, int PARTS>
+__global__ void __launch_bounds__(128) gated_delta_scan_static_kernel(const GatedDeltaParams p) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    constexpr int R = DIM / PARTS;  // rows per lane
+    static_assert(R == kRows, "a lane holds sixteen rows");
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int chunk = p.chunk, cols = p.cols;
+    float* sq = reinterpret_cast<float*>(smem);
+    float* sk = sq + chunk * DIM;
+    float* sg = sk + chunk * DIM;
+    float* sb = sg + chunk * DIM;
+    float* inv_q = sb + chunk;
+    float* inv_k = inv_q + chunk;
+    float* bias = sq + (chunk * (3 * DIM + 3) + 3) / 4 * 4;
+    const int raw_elems = chunk * (3 * DIM + cols);
+    const int raw_bytes = (raw_elems * static_cast<int>(sizeof(scalar_t)) + 15) / 16 * 16;
+    unsigned char* raw_base = reinterpret_cast<unsigned char*>(bias + DIM);
+
+    const int e = blockIdx.x, head = blockIdx.y;
+    const int qk_head = head / (p.n_heads / p.qk_heads);
+    const int col0 = blockIdx.z * cols;
+    const int n_cols = min(cols, p.vdim - col0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+    const int col = tid / PARTS, part = tid % PARTS;
+    const bool active = col < n_cols;
+    const int first = p.first_rows[e], count = p.counts[e];
+    const scalar_t* q = static_cast<const scalar_t*>(p.q) + static_cast<int64_t>(qk_head) * DIM;
+    const scalar_t* k = static_cast<const scalar_t*>(p.k) + static_cast<int64_t>(qk_head) * DIM;
+    const scalar_t* v = static_cast<const scalar_t*>(p.v) + static_cast<int64_t>(head) * p.vdim + col0;
+    const scalar_t* a_pre = static_cast<const scalar_t*>(p.a_pre) + static_cast<int64_t>(head) * DIM;
+    const scalar_t* b_pre = static_cast<const scalar_t*>(p.b_pre) + head;
+    const float rate = expf(p.a_log[head]);
+    float* mine = p.state + ((static_cast<int64_t>(p.slots[e]) * p.n_heads + head) * DIM) * p.vdim + col0;
+
+    load_chunk<scalar_t>(p, reinterpret_cast<scalar_t*>(raw_base), q, k, a_pre, v, first, min(chunk, count), n_cols);
+    for (int i = tid; i < DIM; i += blockDim.x) {
+        bias[i] = p.dt_bias[static_cast<int64_t>(head) * DIM + i];
+    }
+    float S[R];
+#pragma unroll
+    for (int m = 0; m < R; ++m) {
+        S[m] = active ? mine[static_cast<int64_t>(part * R + m) * p.vdim + col] : 0.0f;
+    }
+
+    int buffer = 0;
+    for (int done = 0; done < count; done += chunk, buffer ^= 1) {
+        const int n = min(chunk, count - done);
+        const int64_t t0 = first + done;
+        const scalar_t* raw = reinterpret_cast<const scalar_t*>(raw_base + buffer * raw_bytes);
+        __syncthreads();
+        if (done + chunk < count) {
+            load_chunk<scalar_t>(p, reinterpret_cast<scalar_t*>(raw_base + (buffer ^ 1) * raw_bytes), q, k, a_pre, v,
+                                 t0 + chunk, min(chunk, count - done - chunk), n_cols);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        for (int c = warp; c < n; c += warps) {
+            float b = 0.0f;
+            if (lane == 0) {
+                b = pl_load(b_pre + (t0 + c) * p.b_stride);
+            }
+            const scalar_t* qr = raw + (c * 3) * DIM;
+            const scalar_t* kr = qr + DIM;
+            float qq = 0.0f, kk = 0.0f;
+            for (int i = lane; i < DIM; i += 32) {
+                const float x = pl_load(qr + i), y = pl_load(kr + i);
+                qq = fmaf(x, x, qq);
+                kk = fmaf(y, y, kk);
+            }
+            qq = pl_warp_sum(qq);
+            kk = pl_warp_sum(kk);
+            if (lane == 0) {
+                inv_q[c] = p.q_scale / sqrtf(qq + p.unit_eps);
+                inv_k[c] = 1.0f / sqrtf(kk + p.unit_eps);
+                sb[c] = 1.0f / (1.0f + expf(-b));
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < n * DIM; idx += blockDim.x) {
+            const int c = idx / DIM, i = idx - c * DIM;
+            const scalar_t* token = raw + c * 3 * DIM;
+            sq[idx] = pl_load(token + i) * inv_q[c];
+            sk[idx] = pl_load(token + DIM + i) * inv_k[c];
+            sg[idx] = expf(-rate * softplus_f32(pl_load(token + 2 * DIM + i) + bias[i]));
+        }
+        __syncthreads();
+        const scalar_t* raw_v = raw + chunk * 3 * DIM;
+        // this lane's share of the vectors, one token ahead
+        float4 nq[R / 4], nk[R / 4], ng[R / 4];
+        float nv, nb;
+        auto fetch = [&](int c) {
+            const float4* q4 = reinterpret_cast<const float4*>(sq + c * DIM + part * R);
+            const float4* k4 = reinterpret_cast<const float4*>(sk + c * DIM + part * R);
+            const float4* g4 = reinterpret_cast<const float4*>(sg + c * DIM + part * R);
+#pragma unroll
+            for (int j = 0; j < R / 4; ++j) {
+                nq[j] = q4[j];
+                nk[j] = k4[j];
+                ng[j] = g4[j];
+            }
+            nv = active ? pl_load(raw_v + c * cols + col) : 0.0f;
+            nb = sb[c];
+        };
+        fetch(0);
+        for (int c = 0; c < n; ++c) {
+            float kq[R], kk[R], kg[R];
+#pragma unroll
+            for (int j = 0; j < R / 4; ++j) {
+                kq[4 * j] = nq[j].x; kq[4 * j + 1] = nq[j].y; kq[4 * j + 2] = nq[j].z; kq[4 * j + 3] = nq[j].w;
+                kk[4 * j] = nk[j].x; kk[4 * j + 1] = nk[j].y; kk[4 * j + 2] = nk[j].z; kk[4 * j + 3] = nk[j].w;
+                kg[4 * j] = ng[j].x; kg[4 * j + 1] = ng[j].y; kg[4 * j + 2] = ng[j].z; kg[4 * j + 3] = ng[j].w;
+            }
+            const float vj = nv, beta = nb;
+            if (c + 1 < n) {
+                fetch(c + 1);
+            }
+            float dot0 = 0.0f, dot1 = 0.0f;
+#pragma unroll
+            for (int m = 0; m < R; m += 2) {
+                S[m] *= kg[m];
+                dot0 = fmaf(S[m], kk[m], dot0);
+                S[m + 1] *= kg[m + 1];
+                dot1 = fmaf(S[m + 1], kk[m + 1], dot1);
+            }
+            float dot = dot0 + dot1;
+#pragma unroll
+            for (int offset = PARTS >> 1; offset > 0; offset >>= 1) {
+                dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+            }
+            const float u = beta * (vj - dot);
+            float o0 = 0.0f, o1 = 0.0f;
+#pragma unroll
+            for (int m = 0; m < R; m += 2) {
+                S[m] = fmaf(kk[m], u, S[m]);
+                o0 = fmaf(S[m], kq[m], o0);
+                S[m + 1] = fmaf(kk[m + 1], u, S[m + 1]);
+                o1 = fmaf(S[m + 1], kq[m + 1], o1);
+            }
+            float o = o0 + o1;
+#pragma unroll
+            for (int offset = PARTS >> 1; offset > 0; offset >>= 1) {
+                o += __shfl_xor_sync(0xffffffffu, o, offset);
+            }
+            if (active && part == 0) {
+                p.o_raw[(t0 + c) * (static_cast<int64_t>(p.n_heads) * p.vdim) + static_cast<int64_t>(head) * p.vdim +
+                        col0 + col] = o;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < R; ++m) {
+        if (active) {
+            mine[static_cast<int64_t>(part * R + m) * p.vdim + col] = S[m];
+        }
+    }
+}
+
 // A warp per (token, head): the head's norm over vdim, its weight and the gate.
 template <typename scalar_t>
 __global__ void gated_delta_finish_kernel(const float* __restrict__ o_raw, const float* __restrict__ norm,
@@ -331,7 +496,19 @@ PL_API int pl_gated_delta(const void* q, const void* k, const void* v, int64_t q
             cudaFuncSetAttribute(gated_delta_scan_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem));
         }
-        pl_launch_overlapped(gated_delta_scan_kernel<scalar_t>, grid, dim3(threads), smem, stream, p);
+        // Key sizes 16, 32, 64 and 128 with 128 threads: the form with the sizes known to the compiler.
+        const bool fixed = threads == 128 && (dim == 16 || dim == 32 || dim == 64 || dim == 128) && smem <= 48 * 1024;
+        if (fixed && dim == 16) {
+            pl_launch_overlapped(gated_delta_scan_static_kernel<scalar_t, 16, 1>, grid, dim3(threads), smem, stream, p);
+        } else if (fixed && dim == 32) {
+            pl_launch_overlapped(gated_delta_scan_static_kernel<scalar_t, 32, 2>, grid, dim3(threads), smem, stream, p);
+        } else if (fixed && dim == 64) {
+            pl_launch_overlapped(gated_delta_scan_static_kernel<scalar_t, 64, 4>, grid, dim3(threads), smem, stream, p);
+        } else if (fixed && dim == 128) {
+            pl_launch_overlapped(gated_delta_scan_static_kernel<scalar_t, 128, 8>, grid, dim3(threads), smem, stream, p);
+        } else {
+            pl_launch_overlapped(gated_delta_scan_kernel<scalar_t>, grid, dim3(threads), smem, stream, p);
+        }
         pl_launch_overlapped(gated_delta_finish_kernel<scalar_t>, dim3((n_pairs + 3) / 4), dim3(128), 0, stream,
                              static_cast<const float*>(o_raw), norm, static_cast<const scalar_t*>(gate_pre), gate_stride,
                              static_cast<scalar_t*>(out), out_stride, n_pairs, n_heads, vdim, eps);

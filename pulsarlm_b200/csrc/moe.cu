@@ -19,8 +19,8 @@
 // right for steps of few tokens, where the weights' stream is what costs.
 //
 // pl_moe_sort: the (token, expert) pairs in expert order for the grouped products of long
-// steps: counts per expert, their running sums, and for every pair its row in that order,
-// pairs of one expert in token order. One block.
+// steps: counts per expert, their running sums, and for every pair its row in that order.
+// One block.
 #include "common.cuh"
 
 namespace {
@@ -40,54 +40,74 @@ __device__ __forceinline__ void warp_argmax(float& value, int& index) {
     }
 }
 
-template <typename scalar_t>
+// TOKENS tokens per block (a long step reads the router's weights once per TOKENS tokens): the
+// logits by a warp per expert for all of the block's tokens at once, then a warp per token
+// chooses. A token's sums are the same whatever TOKENS is.
+template <typename scalar_t, int TOKENS>
 __global__ void moe_route_kernel(const scalar_t* __restrict__ h, int64_t h_stride, const float* __restrict__ router,
                                  const float* __restrict__ correction, int32_t* __restrict__ ids,
-                                 float* __restrict__ weights, int hidden, int n_experts, int top, int n_groups,
-                                 int keep) {
+                                 float* __restrict__ weights, int n_tokens, int hidden, int n_experts, int top,
+                                 int n_groups, int keep) {
     pl_grid_trigger();
     pl_grid_wait();
     extern __shared__ float shared[];
-    float* row = shared;                  // [hidden]
-    float* score = row + hidden;          // [n_experts]  s
-    float* choice = score + n_experts;    // [n_experts]  s + correction, -inf once taken or shut out
-    float* group_score = choice + n_experts;  // [n_groups]
-    const int t = blockIdx.x;
+    float* rows = shared;                                   // [TOKENS][hidden]
+    float* scores = rows + TOKENS * hidden;                 // [TOKENS][n_experts]  s
+    float* choices = scores + TOKENS * n_experts;           // [TOKENS][n_experts]  s + correction, -inf once taken or shut out
+    float* group_scores = choices + TOKENS * n_experts;     // [TOKENS][n_groups]
+    const int t0 = blockIdx.x * TOKENS;
+    const int here = min(TOKENS, n_tokens - t0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        row[i] = pl_load(h + t * h_stride + i);
+    for (int i = threadIdx.x; i < TOKENS * hidden; i += blockDim.x) {
+        const int r = i / hidden;
+        rows[i] = r < here ? pl_load(h + static_cast<int64_t>(t0 + r) * h_stride + (i - r * hidden)) : 0.0f;
     }
     __syncthreads();
     const bool vectors = (hidden & 3) == 0 && (reinterpret_cast<uintptr_t>(router) & 15) == 0;
     for (int e = warp; e < n_experts; e += warps) {
         const float* w = router + static_cast<int64_t>(e) * hidden;
-        float z = 0.0f;
+        float z[TOKENS];
+#pragma unroll
+        for (int r = 0; r < TOKENS; ++r) {
+            z[r] = 0.0f;
+        }
         if (vectors) {
-            // (the same products in the same order per lane as the loop below would make with a stride of 4 lanes'
-            // worth: what matters is that the order depends on the width alone)
-#pragma unroll 4
+#pragma unroll 2
             for (int i = lane * 4; i < hidden; i += 128) {
                 const float4 wv = *reinterpret_cast<const float4*>(w + i);
-                const float4 xv = *reinterpret_cast<const float4*>(row + i);
-                z = fmaf(xv.x, wv.x, z);
-                z = fmaf(xv.y, wv.y, z);
-                z = fmaf(xv.z, wv.z, z);
-                z = fmaf(xv.w, wv.w, z);
+#pragma unroll
+                for (int r = 0; r < TOKENS; ++r) {
+                    const float4 xv = *reinterpret_cast<const float4*>(rows + r * hidden + i);
+                    z[r] = fmaf(xv.x, wv.x, z[r]);
+                    z[r] = fmaf(xv.y, wv.y, z[r]);
+                    z[r] = fmaf(xv.z, wv.z, z[r]);
+                    z[r] = fmaf(xv.w, wv.w, z[r]);
+                }
             }
         } else {
             for (int i = lane; i < hidden; i += 32) {
-                z = fmaf(row[i], w[i], z);
+#pragma unroll
+                for (int r = 0; r < TOKENS; ++r) {
+                    z[r] = fmaf(rows[r * hidden + i], w[i], z[r]);
+                }
             }
         }
-        z = pl_warp_sum(z);
-        if (lane == 0) {
-            score[e] = z;
+#pragma unroll
+        for (int r = 0; r < TOKENS; ++r) {
+            const float total = pl_warp_sum(z[r]);
+            if (lane == 0) {
+                scores[r * n_experts + e] = total;
+            }
         }
     }
     __syncthreads();
-    if (warp != 0) {
+    if (warp >= here) {
         return;
     }
+    const int t = t0 + warp;
+    float* score = scores + warp * n_experts;
+    float* choice = choices + warp * n_experts;
+    float* group_score = group_scores + warp * n_groups;
     float top_z = -INFINITY;
     for (int e = lane; e < n_experts; e += 32) {
         top_z = fmaxf(top_z, score[e]);
@@ -381,38 +401,41 @@ __global__ void moe_down_kernel(const scalar_t* __restrict__ act, const scalar_t
     }
 }
 
-// One block: counts, running sums and each pair's row in expert order (pairs of an expert in pair order).
+// One block: counts per expert (shared-memory atomics), their running sums, and each pair's row in
+// expert order. The order of an expert's pairs among themselves is whatever the atomics give:
+// a row's result in the grouped products does not depend on its place.
 __global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int n_pairs, int n_experts,
                                 int32_t* __restrict__ ends, int32_t* __restrict__ row_of_pair,
                                 int32_t* __restrict__ pair_of_row) {
     pl_grid_trigger();
     pl_grid_wait();
-    extern __shared__ int32_t starts[];  // [n_experts + 1]
-    // A thread per expert walks all pairs: few experts, and the order within one stays the pairs' own.
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-        int count = 0;
-        for (int p = 0; p < n_pairs; ++p) {
-            count += ids[p] == e;
+    extern __shared__ int32_t starts[];  // [n_experts + 1] counts, then running sums; [n_experts] cursors
+    int32_t* cursor = starts + n_experts + 1;
+    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) {
+        starts[e] = 0;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < n_experts) {
+            atomicAdd(&starts[e + 1], 1);
         }
-        starts[e + 1] = count;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        starts[0] = 0;
         for (int e = 0; e < n_experts; ++e) {
             starts[e + 1] += starts[e];
             ends[e] = starts[e + 1];
+            cursor[e] = starts[e];
         }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-        int at = starts[e];
-        for (int p = 0; p < n_pairs; ++p) {
-            if (ids[p] == e) {
-                row_of_pair[p] = at;
-                pair_of_row[at] = p;
-                ++at;
-            }
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < n_experts) {
+            const int at = atomicAdd(&cursor[e], 1);
+            row_of_pair[p] = at;
+            pair_of_row[at] = p;
         }
     }
 }
@@ -465,19 +488,35 @@ PL_API int pl_moe_route(const void* h, int64_t h_stride, const float* router, co
                n_experts, n_groups, keep);
     PL_REQUIRE(top <= keep * (n_experts / n_groups), "moe_route: %d experts cannot be chosen from %d groups of %d", top,
                keep, n_experts / n_groups);
-    const size_t smem = (static_cast<size_t>(hidden) + 2 * n_experts + n_groups) * sizeof(float);
-    PL_REQUIRE(smem <= 200 * 1024, "moe_route: hidden %d and %d experts need too much shared memory", hidden, n_experts);
+    const size_t per_token = (static_cast<size_t>(hidden) + 2 * n_experts + n_groups) * sizeof(float);
+    PL_REQUIRE(per_token <= 200 * 1024, "moe_route: hidden %d and %d experts need too much shared memory", hidden,
+               n_experts);
     if (n_tokens == 0) {
         return 0;
     }
+    // Long steps take eight tokens per block when their rows fit (the width must be a multiple of 4
+    // for the rows to stay on 16 bytes).
+    const bool many = n_tokens >= 256 && 8 * per_token <= 200 * 1024 && hidden % 4 == 0;
+    const size_t smem = (many ? 8 : 1) * per_token;
+    const int threads = n_experts > 8 ? 512 : 256;
     PL_DISPATCH_DTYPE(dtype, "moe_route", {
-        if (smem > 48 * 1024) {
-            cudaFuncSetAttribute(moe_route_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem));
+        if (many) {
+            if (smem > 48 * 1024) {
+                cudaFuncSetAttribute(moe_route_kernel<scalar_t, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem));
+            }
+            pl_launch_overlapped(moe_route_kernel<scalar_t, 8>, dim3((n_tokens + 7) / 8), dim3(threads), smem, stream,
+                                 static_cast<const scalar_t*>(h), h_stride, router, correction, ids, weights, n_tokens,
+                                 hidden, n_experts, top, n_groups, keep);
+        } else {
+            if (smem > 48 * 1024) {
+                cudaFuncSetAttribute(moe_route_kernel<scalar_t, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem));
+            }
+            pl_launch_overlapped(moe_route_kernel<scalar_t, 1>, dim3(n_tokens), dim3(threads), smem, stream,
+                                 static_cast<const scalar_t*>(h), h_stride, router, correction, ids, weights, n_tokens,
+                                 hidden, n_experts, top, n_groups, keep);
         }
-        pl_launch_overlapped(moe_route_kernel<scalar_t>, dim3(n_tokens), dim3(n_experts > 8 ? 512 : 256), smem, stream,
-                             static_cast<const scalar_t*>(h), h_stride, router, correction, ids, weights, hidden,
-                             n_experts, top, n_groups, keep);
     });
     PL_CHECK_LAUNCH("moe_route");
     return 0;
@@ -543,8 +582,8 @@ PL_API int pl_moe_sort(const int32_t* ids, int n_pairs, int n_experts, int32_t* 
                        int32_t* pair_of_row, cudaStream_t stream) {
     PL_REQUIRE(n_pairs >= 0 && n_experts > 0 && n_experts <= 8192, "moe_sort: bad sizes pairs=%d experts=%d", n_pairs,
                n_experts);
-    const int threads = n_experts >= 256 ? 256 : ((n_experts + 31) / 32) * 32;
-    pl_launch_overlapped(moe_sort_kernel, dim3(1), dim3(threads), (static_cast<size_t>(n_experts) + 1) * sizeof(int32_t),
+    const int threads = n_pairs >= 1024 ? 1024 : ((n_pairs + 31) / 32) * 32 > 32 ? ((n_pairs + 31) / 32) * 32 : 32;
+    pl_launch_overlapped(moe_sort_kernel, dim3(1), dim3(threads), (2 * static_cast<size_t>(n_experts) + 1) * sizeof(int32_t),
                          stream, ids, n_pairs, n_experts, ends, row_of_pair, pair_of_row);
     PL_CHECK_LAUNCH("moe_sort");
     return 0;

@@ -167,6 +167,60 @@ __global__ void __launch_bounds__(128) short_conv_rows_kernel(
     }
 }
 
+// A step in which every entry brings one row: the convolution and the state's update in one
+// kernel. A thread takes four channels, holds the taps - 1 earlier inputs in registers, writes
+// the row's result and then the state moved up by one with the row's input last. Same
+// products in the same order as the kernels above.
+template <typename scalar_t, int TAPS>
+__global__ void __launch_bounds__(128) short_conv_single_kernel(
+        const scalar_t* __restrict__ h, const float* __restrict__ weight, scalar_t* __restrict__ state,
+        const int32_t* __restrict__ entry, const int32_t* __restrict__ slots, scalar_t* __restrict__ out, int width,
+        int64_t h_stride, int residual, int act) {
+    pl_grid_trigger();
+    constexpr int REACH = TAPS - 1;
+    const int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
+    const int t = blockIdx.x;
+    if (c >= width) {
+        return;
+    }
+    float w[4][TAPS];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+            w[q][j] = weight[static_cast<int64_t>(c + q) * TAPS + j];
+        }
+    }
+    scalar_t* mine = state + static_cast<int64_t>(slots[entry[t]]) * REACH * width + c;
+    pl_grid_wait();
+    float4 window[REACH > 0 ? REACH : 1];
+#pragma unroll
+    for (int j = 0; j < REACH; ++j) {
+        window[j] = pl_load4(mine + static_cast<int64_t>(j) * width);
+    }
+    const float4 own = pl_load4(h + static_cast<int64_t>(t) * h_stride + c);
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int j = 0; j < REACH; ++j) {
+        acc.x = fmaf(w[0][j], window[j].x, acc.x);
+        acc.y = fmaf(w[1][j], window[j].y, acc.y);
+        acc.z = fmaf(w[2][j], window[j].z, acc.z);
+        acc.w = fmaf(w[3][j], window[j].w, acc.w);
+    }
+    acc.x = fmaf(w[0][REACH], own.x, acc.x);
+    acc.y = fmaf(w[1][REACH], own.y, acc.y);
+    acc.z = fmaf(w[2][REACH], own.z, acc.z);
+    acc.w = fmaf(w[3][REACH], own.w, acc.w);
+    pl_store4(out + static_cast<int64_t>(t) * width + c, conv_result(own, acc, residual, act));
+#pragma unroll
+    for (int j = 0; j + 1 < REACH; ++j) {
+        pl_store4(mine + static_cast<int64_t>(j) * width, window[j + 1]);
+    }
+    if (REACH > 0) {
+        pl_store4(mine + static_cast<int64_t>(REACH - 1) * width, own);
+    }
+}
+
 // The state after the step: the last taps - 1 inputs of each sequence. A portion of at least
 // taps - 1 rows writes them from its last rows; a shorter one is handled by its first row's
 // block, which also moves the older rows up.
@@ -315,4 +369,51 @@ PL_API int pl_short_conv_state_strided(const void* h, int64_t h_stride, const in
 PL_API int pl_short_conv_state(const void* h, const int32_t* entry, const int32_t* slots, void* state, int n_tokens,
                                int width, int taps, int dtype, cudaStream_t stream) {
     return pl_short_conv_state_strided(h, width, entry, slots, state, n_tokens, width, taps, dtype, stream);
+}
+
+
+// For a step in which every entry brings exactly one row (the caller vouches for it): the
+// convolution as pl_short_conv_act and the state's update in one launch. Returns 1 without
+// launching when the sizes are not the ones this form takes (taps 2 to 6, a width that is a
+// multiple of 4, rows on 16 bytes): the caller then runs the two kernels.
+PL_API int pl_short_conv_single(const void* h, int64_t h_stride, const float* weight, void* state,
+                                const int32_t* entry, const int32_t* slots, void* out, int n_tokens, int width,
+                                int taps, int residual, int act, int dtype, cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && width > 0 && taps >= 1 && taps <= kMaxTaps && (act == 0 || act == 1),
+               "short_conv_single: bad arguments tokens=%d width=%d taps=%d act=%d", n_tokens, width, taps, act);
+    const bool vectors = width % 4 == 0 && h_stride % 4 == 0 &&
+        ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    if (!vectors || taps < 2 || taps > 6 || (dtype != PL_F32 && dtype != PL_BF16)) {
+        return 1;
+    }
+    if (n_tokens == 0) {
+        return 0;
+    }
+    const dim3 grid(n_tokens, (width / 4 + 127) / 128);
+#define PL_CONV_SINGLE(T)                                                                                          \
+    pl_launch_overlapped(short_conv_single_kernel<scalar_t, T>, grid, dim3(128), 0, stream,                        \
+                         static_cast<const scalar_t*>(h), weight, static_cast<scalar_t*>(state), entry, slots,     \
+                         static_cast<scalar_t*>(out), width, h_stride, residual, act)
+    if (dtype == PL_F32) {
+        using scalar_t = float;
+        switch (taps) {
+            case 2: PL_CONV_SINGLE(2); break;
+            case 3: PL_CONV_SINGLE(3); break;
+            case 4: PL_CONV_SINGLE(4); break;
+            case 5: PL_CONV_SINGLE(5); break;
+            default: PL_CONV_SINGLE(6); break;
+        }
+    } else {
+        using scalar_t = __nv_bfloat16;
+        switch (taps) {
+            case 2: PL_CONV_SINGLE(2); break;
+            case 3: PL_CONV_SINGLE(3); break;
+            case 4: PL_CONV_SINGLE(4); break;
+            case 5: PL_CONV_SINGLE(5); break;
+            default: PL_CONV_SINGLE(6); break;
+        }
+    }
+#undef PL_CONV_SINGLE
+    PL_CHECK_LAUNCH("short_conv_single");
+    return 0;
 }

@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 24
+ABI_VERSION = 25
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -90,6 +90,7 @@ _SIGNATURES = {
                            _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _PTR, _I32, _PTR, _PTR],
     "pl_diff_combine": [_PTR, _PTR, _I32, _I32, _I32, _I32, _F32, _F32, _F32, _I32, _PTR],
     "pl_short_conv_act": [_PTR, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
+    "pl_short_conv_single": [_PTR, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
     "pl_short_conv_state_strided": [_PTR, _I64, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
     "pl_gated_delta": [_PTR, _PTR, _PTR, _I64, _PTR, _I64, _PTR, _I64, _PTR, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR,
                        _PTR, _PTR, _PTR, _I64, _I32, _I32, _I32, _I32, _I32, _I32, _F32, _F32, _F32, _I32, _PTR],
@@ -429,6 +430,28 @@ def short_conv_act(h: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, e
     _call("pl_short_conv_act", _p(h), h.stride(0) if tokens > 1 else width, _p(weight), _p(state), _p(entry),
           _p(slots), _p(out), tokens, width, taps, int(bool(residual)), {"none": 0, "silu": 1}[act], _code(h.dtype),
           _stream())
+
+
+def short_conv_single(h: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, entry: torch.Tensor,
+                      slots: torch.Tensor, out: torch.Tensor, residual: bool, act: str) -> bool:
+    """short_conv_act and the state's update in one launch, for a step in which every entry brings
+    exactly one row. False (nothing launched) when the sizes are not the ones this form takes."""
+    _dev(h, weight, state, entry, slots, out)
+    tokens, width = h.shape
+    taps = weight.shape[1]
+    assert weight.dtype == torch.float32 and weight.shape == (width, taps) and weight.is_contiguous()
+    assert h.stride(1) == 1 and out.is_contiguous() and out.shape == h.shape and out.dtype == h.dtype == state.dtype
+    assert state.is_contiguous() and state.shape[1:] == (taps - 1, width) and out.data_ptr() != h.data_ptr()
+    global _launches
+    code = library().pl_short_conv_single(_p(h), h.stride(0) if tokens > 1 else width, _p(weight), _p(state),
+                                          _p(entry), _p(slots), _p(out), tokens, width, taps, int(bool(residual)),
+                                          {"none": 0, "silu": 1}[act], _code(h.dtype), _stream())
+    if code == 1:
+        return False
+    if code != 0:
+        raise KernelError(library().pl_last_error().decode("utf-8", "replace"))
+    _launches += 1
+    return True
 
 
 def short_conv_state_strided(h: torch.Tensor, entry: torch.Tensor, slots: torch.Tensor, state: torch.Tensor) -> None:

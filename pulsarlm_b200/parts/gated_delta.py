@@ -118,10 +118,14 @@ class ChannelDelta(Part):
         proj = linear(h, self.stacked)                       # [T, c + nh + ra + rg]
         filtered = torch.empty((tokens, c), dtype=h.dtype, device=h.device)
         conv_states = self.filter_state.states(h)
-        ops.short_conv_act(proj[:, :c], self.conv, conv_states, batch.entry, batch.slots, filtered, residual=False,
-                           act="silu")
-        if self.taps > 1:
-            ops.short_conv_state_strided(proj[:, :c], batch.entry, batch.slots, conv_states)
+        # (a step of single tokens: the convolution and its state's update in one launch)
+        single = self.taps > 1 and int(batch.n_decode) == tokens
+        if not (single and ops.short_conv_single(proj[:, :c], self.conv, conv_states, batch.entry, batch.slots,
+                                                 filtered, residual=False, act="silu")):
+            ops.short_conv_act(proj[:, :c], self.conv, conv_states, batch.entry, batch.slots, filtered,
+                               residual=False, act="silu")
+            if self.taps > 1:
+                ops.short_conv_state_strided(proj[:, :c], batch.entry, batch.slots, conv_states)
         b_pre = proj[:, c:c + nh]
         a_pre = linear(proj[:, c + nh:c + nh + self.rank_a], self.a2)
         gate_pre = linear(proj[:, c + nh + self.rank_a:], self.g2)

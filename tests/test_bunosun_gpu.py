@@ -96,6 +96,28 @@ def test_convolution_with_activation_over_columns_of_a_wider_matrix(taps, dtype)
         assert bt.relative_error(torch.cat(got[e]), want[e]) < (1e-5 if dtype == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("taps", [2, 4, 6])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_convolution_and_state_in_one_launch_for_single_tokens(taps, dtype):
+    """Three sequences fed a token a step: the result equals the two-kernel path's bit for bit."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(taps)
+    width, extra, steps = 48, 8, 9
+    full = torch.randn(steps, 3, width + extra, generator=gen).to(dtype).to(DEV)
+    weight = (0.5 * torch.randn(width, taps, generator=gen)).to(DEV)
+    states = [torch.zeros(4, taps - 1, width, dtype=dtype, device=DEV) for _ in range(2)]
+    entry, slots = _i32([0, 1, 2]), _i32([3, 0, 2])
+    for step in range(steps):
+        rows = full[step]
+        outs = [torch.empty(3, width, dtype=dtype, device=DEV) for _ in range(2)]
+        assert ops.short_conv_single(rows[:, :width], weight, states[0], entry, slots, outs[0], residual=False, act="silu")
+        ops.short_conv_act(rows[:, :width], weight, states[1], entry, slots, outs[1], residual=False, act="silu")
+        ops.short_conv_state_strided(rows[:, :width], entry, slots, states[1])
+        assert torch.equal(outs[0], outs[1]) and torch.equal(states[0], states[1])
+    want = plain.causal_conv_silu(full[:, 1, :width].double().cpu(), weight.double().cpu())
+    assert bt.relative_error(outs[0][1].cpu(), want[-1]) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
 @pytest.mark.parametrize("heads,qk_heads,dim,vdim", [(1, 1, 8, 8), (4, 2, 16, 24), (2, 1, 64, 32), (3, 3, 24, 40),
                                                      (2, 2, 128, 128), (1, 1, 40, 200)])
 def test_gated_delta_kernel(heads, qk_heads, dim, vdim):
