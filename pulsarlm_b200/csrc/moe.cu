@@ -278,6 +278,46 @@ __device__ __forceinline__ void warp_dots(const scalar_t* __restrict__ w, int64_
     }
 }
 
+// The same for two sets of rows against two vectors (two experts' rows for one token).
+template <typename scalar_t, int ROWS>
+__device__ __forceinline__ void warp_dots_two(const scalar_t* __restrict__ w0, const float* __restrict__ x0,
+                                              const scalar_t* __restrict__ w1, const float* __restrict__ x1,
+                                              int64_t row_stride, int n, bool vectors, int lane, float (&sums0)[ROWS],
+                                              float (&sums1)[ROWS]) {
+    if (!vectors) {
+        warp_dots<scalar_t, ROWS>(w0, row_stride, x0, n, false, lane, sums0);
+        warp_dots<scalar_t, ROWS>(w1, row_stride, x1, n, false, lane, sums1);
+        return;
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        sums0[r] = 0.0f;
+        sums1[r] = 0.0f;
+    }
+    constexpr int kCount = Vec<scalar_t>::kCount;
+    for (int i = lane * kCount; i < n; i += 32 * kCount) {
+        float a[ROWS][kCount], b[ROWS][kCount];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            Vec<scalar_t>::load(w0 + r * row_stride + i, a[r]);
+            Vec<scalar_t>::load(w1 + r * row_stride + i, b[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+            for (int j = 0; j < kCount; ++j) {
+                sums0[r] = fmaf(a[r][j], x0[i + j], sums0[r]);
+                sums1[r] = fmaf(b[r][j], x1[i + j], sums1[r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        sums0[r] = pl_warp_sum(sums0[r]);
+        sums1[r] = pl_warp_sum(sums1[r]);
+    }
+}
+
 constexpr int kFeaturesPerWarp = 4;
 
 // Block (pair, feature block): act[pair, f] = silu(gate_e[f] . h) * (up_e[f] . h).
@@ -353,18 +393,40 @@ __global__ void moe_down_kernel(const scalar_t* __restrict__ act, const scalar_t
         for (int r = 0; r < kChannelsPerWarp; ++r) {
             sums[r] = 0.0f;
         }
-        for (int j = 0; j < top; ++j) {
-            const int e = ids[static_cast<int64_t>(t) * top + j];
-            if (e < 0 || e >= n_experts) {
-                continue;
+        // Two experts at a time: eight rows' loads in flight per lane. (The sums of an expert's rows are
+        // made as for one expert alone, and added in the experts' order.)
+        for (int j = 0; j < top; j += 2) {
+            const int e0 = ids[static_cast<int64_t>(t) * top + j];
+            const int e1 = j + 1 < top ? ids[static_cast<int64_t>(t) * top + j + 1] : -1;
+            const bool ok0 = e0 >= 0 && e0 < n_experts, ok1 = e1 >= 0 && e1 < n_experts;
+            float dots0[kChannelsPerWarp], dots1[kChannelsPerWarp];
+            if (ok0 && ok1) {
+                warp_dots_two<scalar_t, kChannelsPerWarp>(down + (static_cast<int64_t>(e0) * hidden + c0) * ff, rows + j * ff,
+                                                          down + (static_cast<int64_t>(e1) * hidden + c0) * ff,
+                                                          rows + (j + 1) * ff, ff, ff, vectors, lane, dots0, dots1);
+            } else {
+                if (ok0) {
+                    warp_dots<scalar_t, kChannelsPerWarp>(down + (static_cast<int64_t>(e0) * hidden + c0) * ff, ff,
+                                                          rows + j * ff, ff, vectors, lane, dots0);
+                }
+                if (ok1) {
+                    warp_dots<scalar_t, kChannelsPerWarp>(down + (static_cast<int64_t>(e1) * hidden + c0) * ff, ff,
+                                                          rows + (j + 1) * ff, ff, vectors, lane, dots1);
+                }
             }
-            float dots[kChannelsPerWarp];
-            warp_dots<scalar_t, kChannelsPerWarp>(down + (static_cast<int64_t>(e) * hidden + c0) * ff, ff, rows + j * ff, ff,
-                                                  vectors, lane, dots);
-            const float weight = weights[static_cast<int64_t>(t) * top + j];
+            if (ok0) {
+                const float weight = weights[static_cast<int64_t>(t) * top + j];
 #pragma unroll
-            for (int r = 0; r < kChannelsPerWarp; ++r) {
-                sums[r] = fmaf(weight, dots[r], sums[r]);
+                for (int r = 0; r < kChannelsPerWarp; ++r) {
+                    sums[r] = fmaf(weight, dots0[r], sums[r]);
+                }
+            }
+            if (ok1) {
+                const float weight = weights[static_cast<int64_t>(t) * top + j + 1];
+#pragma unroll
+                for (int r = 0; r < kChannelsPerWarp; ++r) {
+                    sums[r] = fmaf(weight, dots1[r], sums[r]);
+                }
             }
         }
         if (lane < kChannelsPerWarp) {
