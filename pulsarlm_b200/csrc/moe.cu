@@ -72,16 +72,29 @@ __global__ void moe_route_kernel(const scalar_t* __restrict__ h, int64_t h_strid
             z[r] = 0.0f;
         }
         if (vectors) {
-#pragma unroll 2
-            for (int i = lane * 4; i < hidden; i += 128) {
-                const float4 wv = *reinterpret_cast<const float4*>(w + i);
+            // Eight of the lane's vectors of the expert's row are asked for before any is used (the row
+            // comes from L2 or memory: one load at a time would make a chain of their latencies).
+            constexpr int kAhead = 8;
+            for (int base = lane * 4; base < hidden; base += 128 * kAhead) {
+                float4 wv[kAhead];
 #pragma unroll
-                for (int r = 0; r < TOKENS; ++r) {
-                    const float4 xv = *reinterpret_cast<const float4*>(rows + r * hidden + i);
-                    z[r] = fmaf(xv.x, wv.x, z[r]);
-                    z[r] = fmaf(xv.y, wv.y, z[r]);
-                    z[r] = fmaf(xv.z, wv.z, z[r]);
-                    z[r] = fmaf(xv.w, wv.w, z[r]);
+                for (int u = 0; u < kAhead; ++u) {
+                    const int i = base + 128 * u;
+                    wv[u] = i < hidden ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+#pragma unroll
+                for (int u = 0; u < kAhead; ++u) {
+                    const int i = base + 128 * u;
+                    if (i < hidden) {
+#pragma unroll
+                        for (int r = 0; r < TOKENS; ++r) {
+                            const float4 xv = *reinterpret_cast<const float4*>(rows + r * hidden + i);
+                            z[r] = fmaf(xv.x, wv[u].x, z[r]);
+                            z[r] = fmaf(xv.y, wv[u].y, z[r]);
+                            z[r] = fmaf(xv.z, wv[u].z, z[r]);
+                            z[r] = fmaf(xv.w, wv[u].w, z[r]);
+                        }
+                    }
                 }
             }
         } else {
@@ -506,11 +519,20 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int n_pairs, in
 template <typename scalar_t>
 __global__ void moe_gather_kernel(const scalar_t* __restrict__ x, int64_t x_stride,
                                   const int32_t* __restrict__ pair_of_row, scalar_t* __restrict__ sorted, int hidden,
-                                  int top) {
+                                  int top, int vectors) {
     pl_grid_trigger();
     pl_grid_wait();
     const int r = blockIdx.x;
     const int64_t t = pair_of_row[r] / top;
+    constexpr int kPer = 16 / sizeof(scalar_t);
+    if (vectors) {
+        const uint4* from = reinterpret_cast<const uint4*>(x + t * x_stride);
+        uint4* to = reinterpret_cast<uint4*>(sorted + static_cast<int64_t>(r) * hidden);
+        for (int i = threadIdx.x; i < hidden / kPer; i += blockDim.x) {
+            to[i] = from[i];
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         sorted[static_cast<int64_t>(r) * hidden + i] = x[t * x_stride + i];
     }
@@ -520,10 +542,33 @@ __global__ void moe_gather_kernel(const scalar_t* __restrict__ x, int64_t x_stri
 template <typename scalar_t>
 __global__ void moe_combine_kernel(const scalar_t* __restrict__ y, const int32_t* __restrict__ row_of_pair,
                                    const float* __restrict__ weights, const scalar_t* __restrict__ also,
-                                   scalar_t* __restrict__ out, int hidden, int top) {
+                                   scalar_t* __restrict__ out, int hidden, int top, int vectors) {
     pl_grid_trigger();
     pl_grid_wait();
     const int64_t t = blockIdx.x;
+    if (vectors) {
+        // (the same sums, four channels at a time)
+        for (int i = 4 * threadIdx.x; i < hidden; i += 4 * blockDim.x) {
+            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int j = 0; j < top; ++j) {
+                const float weight = weights[t * top + j];
+                const float4 v = pl_load4(y + static_cast<int64_t>(row_of_pair[t * top + j]) * hidden + i);
+                sum.x = fmaf(weight, v.x, sum.x);
+                sum.y = fmaf(weight, v.y, sum.y);
+                sum.z = fmaf(weight, v.z, sum.z);
+                sum.w = fmaf(weight, v.w, sum.w);
+            }
+            if (also != nullptr) {
+                const float4 v = pl_load4(also + t * hidden + i);
+                sum.x += v.x;
+                sum.y += v.y;
+                sum.z += v.z;
+                sum.w += v.w;
+            }
+            pl_store4(out + t * hidden + i, sum);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float sum = 0.0f;
         for (int j = 0; j < top; ++j) {
@@ -658,9 +703,12 @@ PL_API int pl_moe_gather(const void* x, int64_t x_stride, const int32_t* pair_of
         return 0;
     }
     PL_DISPATCH_DTYPE(dtype, "moe_gather", {
-        pl_launch_overlapped(moe_gather_kernel<scalar_t>, dim3(n_pairs), dim3(hidden >= 1024 ? 256 : 128), 0, stream,
+        constexpr int kPer = 16 / sizeof(scalar_t);
+        const int vectors = hidden % kPer == 0 && x_stride % kPer == 0 &&
+            ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(sorted)) & 15) == 0;
+        pl_launch_overlapped(moe_gather_kernel<scalar_t>, dim3(n_pairs), dim3(hidden >= 2048 ? 256 : 128), 0, stream,
                              static_cast<const scalar_t*>(x), x_stride, pair_of_row, static_cast<scalar_t*>(sorted),
-                             hidden, top);
+                             hidden, top, vectors);
     });
     PL_CHECK_LAUNCH("moe_gather");
     return 0;
@@ -673,9 +721,11 @@ PL_API int pl_moe_combine(const void* y, const int32_t* row_of_pair, const float
         return 0;
     }
     PL_DISPATCH_DTYPE(dtype, "moe_combine", {
+        const int vectors = hidden % 4 == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(also) |
+                                                 reinterpret_cast<uintptr_t>(out)) & 15) == 0;
         pl_launch_overlapped(moe_combine_kernel<scalar_t>, dim3(n_tokens), dim3(hidden >= 1024 ? 256 : 128), 0, stream,
                              static_cast<const scalar_t*>(y), row_of_pair, weights, static_cast<const scalar_t*>(also),
-                             static_cast<scalar_t*>(out), hidden, top);
+                             static_cast<scalar_t*>(out), hidden, top, vectors);
     });
     PL_CHECK_LAUNCH("moe_combine");
     return 0;

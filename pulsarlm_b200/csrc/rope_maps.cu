@@ -30,6 +30,13 @@ __device__ __forceinline__ float rotated(const scalar_t* x, int e, int rotary, c
     return (e & 1) ? rope_hi(lo, hi, cs[i], sn[i]) : rope_lo(lo, hi, cs[i], sn[i]);
 }
 
+__device__ __forceinline__ void store_pair(float* p, float lo, float hi) {
+    *reinterpret_cast<float2*>(p) = make_float2(lo, hi);
+}
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float lo, float hi) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(lo, hi);
+}
+
 template <typename scalar_t>
 __global__ void rope_maps_write_kernel(const scalar_t* __restrict__ q, const scalar_t* __restrict__ k,
                                        const scalar_t* __restrict__ v, int64_t row_stride,
@@ -65,15 +72,38 @@ __global__ void rope_maps_write_kernel(const scalar_t* __restrict__ q, const sca
     const int row0 = blockIdx.y * rows_per_block, row1 = min(row0 + rows_per_block, q_rows + n_kv_heads);
     const scalar_t* qt = q + t * row_stride;
     scalar_t* qo = q_out + static_cast<int64_t>(t) * q_rows * padded;
-    for (int idx = row0 * padded + threadIdx.x; idx < min(row1, q_rows) * padded; idx += blockDim.x) {
-        const int hm = idx / padded, d = idx % padded;
-        const int m = hm % maps;
-        const int e = d - m * dim;
-        float value = 0.0f;
-        if (e >= 0 && e < dim) {
-            value = rotated(qt + static_cast<int64_t>(hm) * dim, e, rotary, cs, sn);
+    if ((dim & 1) == 0) {
+        // Two neighbouring columns per thread: a rotary pair is read once and both its halves stored.
+        const int half_row = padded / 2;
+        for (int idx = row0 * half_row + threadIdx.x; idx < min(row1, q_rows) * half_row; idx += blockDim.x) {
+            const int hm = idx / half_row, d = 2 * (idx % half_row);
+            const int m = hm % maps;
+            const int e = d - m * dim;
+            float lo = 0.0f, hi = 0.0f;
+            if (e >= 0 && e < dim) {
+                const scalar_t* x = qt + static_cast<int64_t>(hm) * dim + e;
+                lo = pl_load(x);
+                hi = pl_load(x + 1);
+                if (e < rotary) {
+                    const float c = cs[e >> 1], s = sn[e >> 1];
+                    const float a = rope_lo(lo, hi, c, s), b = rope_hi(lo, hi, c, s);
+                    lo = a;
+                    hi = b;
+                }
+            }
+            store_pair(qo + static_cast<int64_t>(hm) * padded + d, lo, hi);
         }
-        pl_store(qo + idx, value);
+    } else {
+        for (int idx = row0 * padded + threadIdx.x; idx < min(row1, q_rows) * padded; idx += blockDim.x) {
+            const int hm = idx / padded, d = idx % padded;
+            const int m = hm % maps;
+            const int e = d - m * dim;
+            float value = 0.0f;
+            if (e >= 0 && e < dim) {
+                value = rotated(qt + static_cast<int64_t>(hm) * dim, e, rotary, cs, sn);
+            }
+            pl_store(qo + idx, value);
+        }
     }
     if (page < 0 || row1 <= q_rows) {
         return;
