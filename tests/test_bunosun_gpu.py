@@ -182,17 +182,18 @@ def test_router_chooses_as_the_plain_one(experts, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("tokens", [1, 7, 150])
-def test_routed_experts_pair_by_pair_and_grouped(dtype, tokens, monkeypatch):
-    """The part alone: few tokens stream their experts' weights; many (bfloat16) are sorted by expert."""
+@pytest.mark.parametrize("tokens,experts,top", [(1, 10, 3), (7, 10, 3), (150, 10, 3), (50, 80, 1), (300, 5, 5)])
+def test_routed_experts_pair_by_pair_and_grouped(dtype, tokens, experts, top, monkeypatch):
+    """The part alone: few tokens stream their experts' weights; many (bfloat16) are sorted by expert
+    (also with more experts than tokens, so that most experts get no row, and with every expert chosen)."""
     from pulsarlm_b200.parts import moe as moe_part
     from pulsarlm_b200.parts.registry import BuildContext
     from pulsarlm_b200.parts.spec import PartSpec
 
     _ops()
     gen = torch.Generator().manual_seed(tokens)
-    hidden, ff, experts, top = 64, 40, 10, 3
-    mlp = {"router": {"experts": experts, "top": top, "groups": {"count": 5, "keep": 3}}, "shared": {"ff": 24}}
+    hidden, ff = 64, 40
+    mlp = {"router": {"experts": experts, "top": top, "groups": {"count": 5, "keep": 3 if top < 5 else 5}}, "shared": {"ff": 24}}
     w = {"m.router": torch.randn(experts, hidden, generator=gen) * 0.5, "m.correction": 0.1 * torch.randn(experts, generator=gen)}
     for name, size in [(f"e{e}", ff) for e in range(experts)] + [("shared", 24)]:
         w[f"m.{name}.gate"] = (torch.randn(size, hidden, generator=gen) / hidden ** 0.5).to(dtype)
@@ -201,7 +202,7 @@ def test_routed_experts_pair_by_pair_and_grouped(dtype, tokens, monkeypatch):
     h = torch.randn(tokens, hidden, generator=gen).to(dtype)
     want = plain.routed_experts(mlp, {k: v.double() for k, v in w.items()}, "m.", h.double())
     spec = PartSpec("moe", {"hidden_size": hidden, "expert_size": ff, "n_experts": experts, "top": top, "groups": 5,
-                            "keep_groups": 3, "shared_size": 24},
+                            "keep_groups": mlp["router"]["groups"]["keep"], "shared_size": 24},
                     {"router": "m.router", "correction": "m.correction", "expert_gate": "m.e{e}.gate",
                      "expert_up": "m.e{e}.up", "expert_down": "m.e{e}.down", "shared_gate": "m.shared.gate",
                      "shared_up": "m.shared.up", "shared_down": "m.shared.down"})
@@ -511,6 +512,23 @@ def test_configurations_drawn_at_random(seed):
         tm.check(tokens, harness.replay(runner, steps), f"random configuration {seed}")
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(8, 1, 16, 32), (10, 1, 8, 16), (4, 4, 64, 128), (2, 1, 72, 96),
+                                                     (1, 1, 128, 256)])
+def test_head_counts_and_row_sizes_with_and_without_a_tensor_core_kernel(heads, kv_heads, dim, vdim):
+    """Sixteen and twenty query rows per kv head, rows of 128, of 144 and of 256: prompts, portions and
+    single tokens in bfloat16 and float32."""
+    cfg = {"architecture": "Bunosun", "vocab": 71, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+           "layers": [bt.attention_layer(heads, kv_heads, dim, vdim, 37, min(dim, 8), None, diff=0.4,
+                                         scale=dim ** -0.5, factor=2.0)]}
+    for dtype in ("float32", "bfloat16"):
+        tm = bt.TinyBunosun("-", dtype, cfg=cfg, seed=3)
+        tokens = {"p": bt.random_tokens(cfg, 100, 60), "q": bt.random_tokens(cfg, 20, 61)}
+        steps = [([("p", tokens["p"][:70], list(range(70))), ("q", tokens["q"][:1], [0])], []),
+                 ([("p", tokens["p"][70:71], [0]), ("q", tokens["q"][1:19], list(range(18)))], [])]
+        steps += [([("p", [tokens["p"][i]], [0])] + ([("q", [tokens["q"][19]], [0])] if i == 71 else []), []) for i in range(71, 100)]
+        tm.check(tokens, harness.replay(tm.runner(16), steps), f"heads {heads}/{kv_heads} of {dim}, {vdim}")
+
+
 def test_missing_and_misshapen_tensors_are_named():
     from pulsarlm_b200.engine.loading import load_model
     from pulsarlm_b200.weights.loader import WeightsError
@@ -554,6 +572,24 @@ def test_greedy_generation_through_the_engine(cuda_graphs):
         assert list(request.output) == _plain_greedy(tm, prompt, 12)
     if cuda_graphs:
         assert engine.runner.graph_steps > 0
+
+
+def test_many_requests_decode_in_captured_steps_through_the_grouped_experts():
+    """Sixty requests at once in bfloat16: their decode steps are long enough for the experts' sorted
+    path, inside captured steps; every request ends with as many tokens as asked."""
+    from pulsarlm_b200.engine.engine import Engine
+
+    tm = _model("A", "bfloat16")
+    engine = Engine(tm.folder, dtype="bfloat16", device=DEV, page_size=16, n_pages=200, max_requests=60,
+                    prefill_tokens_per_step=256, cuda_graphs=True)
+    prompts = [bt.random_tokens(tm.cfg, 3 + i % 4, 200 + i) for i in range(60)]
+    requests = [engine.submit(p, max_tokens=6, ignore_eos=True) for p in prompts]
+    for _ in range(400):
+        if not engine.has_work():
+            break
+        engine.step()
+    assert not engine.has_work() and engine.runner.graph_steps > 0
+    assert all(len(r.output) == 6 and r.finish_reason == "length" for r in requests)
 
 
 def test_engine_preempts_and_recomputes_with_states():
