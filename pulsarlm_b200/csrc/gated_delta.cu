@@ -97,6 +97,50 @@ __device__ __forceinline__ void load_chunk(const GatedDeltaParams& p, scalar_t* 
     cp_async_commit();
 }
 
+// The same by `threads` threads numbered `tid` (one half of a CTA), with the sizes given.
+template <typename scalar_t>
+__device__ __forceinline__ void load_chunk_by(const GatedDeltaParams& p, scalar_t* raw, const scalar_t* q,
+                                              const scalar_t* k, const scalar_t* a_pre, const scalar_t* v, int64_t t0,
+                                              int n, int n_cols, int tid, int threads, int dim, int cols) {
+    scalar_t* raw_v = raw + p.chunk * 3 * dim;
+    if (p.async_loads) {
+        constexpr int kPer = 16 / sizeof(scalar_t);
+        const int gv = dim / kPer, gc = cols / kPer;
+        const int per_token = 3 * gv + gc;
+        for (int idx = tid; idx < n * per_token; idx += threads) {
+            const int c = idx / per_token, g = idx % per_token;
+            if (g < 3 * gv) {
+                const int which = g / gv, e = (g % gv) * kPer;
+                const scalar_t* src = which == 0 ? q + (t0 + c) * p.qkv_stride
+                                    : which == 1 ? k + (t0 + c) * p.qkv_stride : a_pre + (t0 + c) * p.a_stride;
+                cp_async_16(raw + (c * 3 + which) * dim + e, src + e);
+            } else {
+                const int e = (g - 3 * gv) * kPer;
+                if (e < n_cols) {
+                    cp_async_16(raw_v + c * cols + e, v + (t0 + c) * p.qkv_stride + e);
+                }
+            }
+        }
+    } else {
+        const int per_token = 3 * dim + cols;
+        for (int idx = tid; idx < n * per_token; idx += threads) {
+            const int c = idx / per_token, g = idx % per_token;
+            if (g < 3 * dim) {
+                const int which = g / dim, e = g % dim;
+                const scalar_t* src = which == 0 ? q + (t0 + c) * p.qkv_stride
+                                    : which == 1 ? k + (t0 + c) * p.qkv_stride : a_pre + (t0 + c) * p.a_stride;
+                raw[(c * 3 + which) * dim + e] = src[e];
+            } else {
+                const int e = g - 3 * dim;
+                if (e < n_cols) {
+                    raw_v[c * cols + e] = v[(t0 + c) * p.qkv_stride + e];
+                }
+            }
+        }
+    }
+    cp_async_commit();
+}
+
 template <typename scalar_t>
 __global__ void __launch_bounds__(512) gated_delta_scan_kernel(const GatedDeltaParams p) {
     pl_grid_trigger();
@@ -243,13 +287,221 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(const GatedDeltaP
     }
 }
 
-// The same scan with the key size and the lanes per column known to the compiler: a lane holds
+// The same scan with the key size and the lanes per column known to the compiler, and with the
+// work split between two halves of the CTA: warps 0 to 3 hold the state's columns (a lane holds
 // DIM / PARTS = 16 consecutive rows of its column, reads its share of q^, k^ and g with 16-byte
-// loads, and fetches them one token ahead of the token whose chain it is in. (A lane's rows
-// differ from the kernel above, so the sums' order does; which kernel runs depends on the
-// sizes alone.)
+// loads one token ahead of the token whose chain it is in) and do nothing but the tokens'
+// updates, one chunk after the other; warps 4 to 7 meanwhile make the next chunk ready: they
+// ask for the chunk after it (cp.async), turn the one that has arrived into the fp32 vectors
+// (the unit factors by a few lanes per token, all of a chunk's tokens at once; the
+// exponentials one (token, channel) per thread) and leave them in the other of two buffers.
+// The halves meet once a chunk. What bounds the scan is then the chain of one token's update
+// alone. (A lane's rows differ from the kernel above, so the sums' order does; which kernel
+// runs depends on the sizes alone.)
 template <typename scalar_t, int DIM, int PARTS>
-__global__ void __launch_bounds__(128) gated_delta_scan_static_kernel(const GatedDeltaParams p) {
+__global__ void __launch_bounds__(256) gated_delta_scan_static_kernel(const GatedDeltaParams p) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    constexpr int R = DIM / PARTS;      // rows per lane
+    constexpr int COLS = 128 / PARTS;   // value columns per CTA
+    static_assert(R == kRows, "a lane holds sixteen rows");
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int chunk = p.chunk;
+    // two buffers of a chunk's vectors: [chunk][DIM] q^, k^, g, [chunk][COLS] v, [chunk] b (rounded up to 4 floats)
+    const int vec_floats = (chunk * (3 * DIM + COLS + 1) + 3) / 4 * 4;
+    float* vec_base = reinterpret_cast<float*>(smem);
+    float* inv_q = vec_base + 2 * vec_floats;   // [chunk]
+    float* inv_k = inv_q + chunk;               // [chunk]
+    float* bias = inv_q + (2 * chunk + 3) / 4 * 4;  // [DIM]
+    const int raw_elems = chunk * (3 * DIM + COLS);
+    const int raw_bytes = (raw_elems * static_cast<int>(sizeof(scalar_t)) + 15) / 16 * 16;
+    unsigned char* raw_base = reinterpret_cast<unsigned char*>(bias + DIM);
+
+    const int e = blockIdx.x, head = blockIdx.y;
+    const int qk_head = head / (p.n_heads / p.qk_heads);
+    const int col0 = blockIdx.z * COLS;
+    const int n_cols = min(COLS, p.vdim - col0);
+    const int tid = threadIdx.x;
+    const bool producer = tid >= 128;
+    const int first = p.first_rows[e], count = p.counts[e];
+    const int n_chunks = (count + chunk - 1) / chunk;
+    const scalar_t* q = static_cast<const scalar_t*>(p.q) + static_cast<int64_t>(qk_head) * DIM;
+    const scalar_t* k = static_cast<const scalar_t*>(p.k) + static_cast<int64_t>(qk_head) * DIM;
+    const scalar_t* v = static_cast<const scalar_t*>(p.v) + static_cast<int64_t>(head) * p.vdim + col0;
+    const scalar_t* a_pre = static_cast<const scalar_t*>(p.a_pre) + static_cast<int64_t>(head) * DIM;
+    const scalar_t* b_pre = static_cast<const scalar_t*>(p.b_pre) + head;
+
+    // ---- the consumers' state
+    const int col = tid / PARTS, part = tid % PARTS;
+    const bool active = !producer && col < n_cols;
+    float* mine = p.state + ((static_cast<int64_t>(p.slots[e]) * p.n_heads + head) * DIM) * p.vdim + col0;
+    float S[R];
+#pragma unroll
+    for (int m = 0; m < R; ++m) {
+        S[m] = active ? mine[static_cast<int64_t>(part * R + m) * p.vdim + col] : 0.0f;
+    }
+    // ---- the producers' constants
+    const int ptid = tid - 128;
+    const float rate = expf(p.a_log[head]);
+    if (producer) {
+        for (int i = ptid; i < DIM; i += 128) {
+            bias[i] = p.dt_bias[static_cast<int64_t>(head) * DIM + i];
+        }
+        if (n_chunks > 0) {
+            load_chunk_by<scalar_t>(p, reinterpret_cast<scalar_t*>(raw_base), q, k, a_pre, v, first, min(chunk, count),
+                                    n_cols, ptid, 128, DIM, COLS);
+        }
+    }
+    // lanes per token for the unit factors: all of a chunk's tokens at once
+    const int group = min(32, 128 / chunk);
+
+    for (int i = -1; i < n_chunks; ++i) {
+        if (producer) {
+            const int next = i + 1;
+            if (next < n_chunks) {
+                const int n = min(chunk, count - next * chunk);
+                const int64_t t0 = first + static_cast<int64_t>(next) * chunk;
+                if (next + 1 < n_chunks) {
+                    load_chunk_by<scalar_t>(p, reinterpret_cast<scalar_t*>(raw_base + ((next + 1) & 1) * raw_bytes), q, k,
+                                            a_pre, v, t0 + chunk, min(chunk, count - (next + 1) * chunk), n_cols, ptid,
+                                            128, DIM, COLS);
+                    cp_async_wait<1>();
+                } else {
+                    cp_async_wait<0>();
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const scalar_t* raw = reinterpret_cast<const scalar_t*>(raw_base + (next & 1) * raw_bytes);
+                float* sq = vec_base + (next & 1) * vec_floats;
+                float* sk = sq + chunk * DIM;
+                float* sg = sk + chunk * DIM;
+                float* sv = sg + chunk * DIM;
+                float* sb = sv + chunk * COLS;
+                {
+                    const int c = ptid / group, sub = ptid % group;
+                    float qq = 0.0f, kk = 0.0f, b = 0.0f;
+                    if (c < n) {
+                        if (sub == 0) {
+                            b = pl_load(b_pre + (t0 + c) * p.b_stride);
+                        }
+                        const scalar_t* qr = raw + (c * 3) * DIM;
+                        const scalar_t* kr = qr + DIM;
+                        for (int j = sub; j < DIM; j += group) {
+                            const float x = pl_load(qr + j), y = pl_load(kr + j);
+                            qq = fmaf(x, x, qq);
+                            kk = fmaf(y, y, kk);
+                        }
+                    }
+                    for (int offset = group >> 1; offset > 0; offset >>= 1) {
+                        qq += __shfl_xor_sync(0xffffffffu, qq, offset);
+                        kk += __shfl_xor_sync(0xffffffffu, kk, offset);
+                    }
+                    if (c < n && sub == 0) {
+                        inv_q[c] = p.q_scale / sqrtf(qq + p.unit_eps);
+                        inv_k[c] = 1.0f / sqrtf(kk + p.unit_eps);
+                        sb[c] = 1.0f / (1.0f + expf(-b));
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                for (int idx = ptid; idx < n * DIM; idx += 128) {
+                    const int c = idx / DIM, j = idx - c * DIM;
+                    const scalar_t* token = raw + c * 3 * DIM;
+                    sq[idx] = pl_load(token + j) * inv_q[c];
+                    sk[idx] = pl_load(token + DIM + j) * inv_k[c];
+                    sg[idx] = expf(-rate * softplus_f32(pl_load(token + 2 * DIM + j) + bias[j]));
+                }
+                const scalar_t* raw_v = raw + chunk * 3 * DIM;
+                for (int idx = ptid; idx < n * COLS; idx += 128) {
+                    const int j = idx % COLS;
+                    sv[idx] = j < n_cols ? pl_load(raw_v + idx) : 0.0f;
+                }
+            }
+        } else if (i >= 0) {
+            const int n = min(chunk, count - i * chunk);
+            const int64_t t0 = first + static_cast<int64_t>(i) * chunk;
+            const float* sq = vec_base + (i & 1) * vec_floats;
+            const float* sk = sq + chunk * DIM;
+            const float* sg = sk + chunk * DIM;
+            const float* sv = sg + chunk * DIM;
+            const float* sb = sv + chunk * COLS;
+            // this lane's share of the vectors, one token ahead
+            float4 nq[R / 4], nk[R / 4], ng[R / 4];
+            float nv, nb;
+            auto fetch = [&](int c) {
+                const float4* q4 = reinterpret_cast<const float4*>(sq + c * DIM + part * R);
+                const float4* k4 = reinterpret_cast<const float4*>(sk + c * DIM + part * R);
+                const float4* g4 = reinterpret_cast<const float4*>(sg + c * DIM + part * R);
+#pragma unroll
+                for (int j = 0; j < R / 4; ++j) {
+                    nq[j] = q4[j];
+                    nk[j] = k4[j];
+                    ng[j] = g4[j];
+                }
+                nv = sv[c * COLS + col];
+                nb = sb[c];
+            };
+            fetch(0);
+            for (int c = 0; c < n; ++c) {
+                float kq[R], kk[R], kg[R];
+#pragma unroll
+                for (int j = 0; j < R / 4; ++j) {
+                    kq[4 * j] = nq[j].x; kq[4 * j + 1] = nq[j].y; kq[4 * j + 2] = nq[j].z; kq[4 * j + 3] = nq[j].w;
+                    kk[4 * j] = nk[j].x; kk[4 * j + 1] = nk[j].y; kk[4 * j + 2] = nk[j].z; kk[4 * j + 3] = nk[j].w;
+                    kg[4 * j] = ng[j].x; kg[4 * j + 1] = ng[j].y; kg[4 * j + 2] = ng[j].z; kg[4 * j + 3] = ng[j].w;
+                }
+                const float vj = nv, beta = nb;
+                if (c + 1 < n) {
+                    fetch(c + 1);
+                }
+                float dot0 = 0.0f, dot1 = 0.0f;
+#pragma unroll
+                for (int m = 0; m < R; m += 2) {
+                    S[m] *= kg[m];
+                    dot0 = fmaf(S[m], kk[m], dot0);
+                    S[m + 1] *= kg[m + 1];
+                    dot1 = fmaf(S[m + 1], kk[m + 1], dot1);
+                }
+                float dot = dot0 + dot1;
+#pragma unroll
+                for (int offset = PARTS >> 1; offset > 0; offset >>= 1) {
+                    dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+                }
+                const float u = beta * (vj - dot);
+                float o0 = 0.0f, o1 = 0.0f;
+#pragma unroll
+                for (int m = 0; m < R; m += 2) {
+                    S[m] = fmaf(kk[m], u, S[m]);
+                    o0 = fmaf(S[m], kq[m], o0);
+                    S[m + 1] = fmaf(kk[m + 1], u, S[m + 1]);
+                    o1 = fmaf(S[m + 1], kq[m + 1], o1);
+                }
+                float o = o0 + o1;
+#pragma unroll
+                for (int offset = PARTS >> 1; offset > 0; offset >>= 1) {
+                    o += __shfl_xor_sync(0xffffffffu, o, offset);
+                }
+                if (active && part == 0) {
+                    p.o_raw[(t0 + c) * (static_cast<int64_t>(p.n_heads) * p.vdim) + static_cast<int64_t>(head) * p.vdim +
+                            col0 + col] = o;
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int m = 0; m < R; ++m) {
+        if (active) {
+            mine[static_cast<int64_t>(part * R + m) * p.vdim + col] = S[m];
+        }
+    }
+}
+
+// The form for steps that bring a token or two per entry (steps of single tokens): the same
+// arithmetic by one half alone, 128 threads that make a chunk ready and then walk it. There is
+// nothing to overlap in such a step, and three of these CTAs fit where one of the above does.
+// Same products and sums in the same order as the kernel above: a token's result does not depend
+// on which of the two ran.
+template <typename scalar_t, int DIM, int PARTS>
+__global__ void __launch_bounds__(128) gated_delta_scan_static_single_kernel(const GatedDeltaParams p) {
     pl_grid_trigger();
     pl_grid_wait();
     constexpr int R = DIM / PARTS;  // rows per lane
@@ -271,7 +523,7 @@ __global__ void __launch_bounds__(128) gated_delta_scan_static_kernel(const Gate
     const int qk_head = head / (p.n_heads / p.qk_heads);
     const int col0 = blockIdx.z * cols;
     const int n_cols = min(cols, p.vdim - col0);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+    const int tid = threadIdx.x;
     const int col = tid / PARTS, part = tid % PARTS;
     const bool active = col < n_cols;
     const int first = p.first_rows[e], count = p.counts[e];
@@ -307,22 +559,27 @@ __global__ void __launch_bounds__(128) gated_delta_scan_static_kernel(const Gate
             cp_async_wait<0>();
         }
         __syncthreads();
-        for (int c = warp; c < n; c += warps) {
-            float b = 0.0f;
-            if (lane == 0) {
-                b = pl_load(b_pre + (t0 + c) * p.b_stride);
+        {
+            const int group = min(32, 128 / chunk);
+            const int c = tid / group, sub = tid % group;
+            float qq = 0.0f, kk = 0.0f, b = 0.0f;
+            if (c < n) {
+                if (sub == 0) {
+                    b = pl_load(b_pre + (t0 + c) * p.b_stride);
+                }
+                const scalar_t* qr = raw + (c * 3) * DIM;
+                const scalar_t* kr = qr + DIM;
+                for (int j = sub; j < DIM; j += group) {
+                    const float x = pl_load(qr + j), y = pl_load(kr + j);
+                    qq = fmaf(x, x, qq);
+                    kk = fmaf(y, y, kk);
+                }
             }
-            const scalar_t* qr = raw + (c * 3) * DIM;
-            const scalar_t* kr = qr + DIM;
-            float qq = 0.0f, kk = 0.0f;
-            for (int i = lane; i < DIM; i += 32) {
-                const float x = pl_load(qr + i), y = pl_load(kr + i);
-                qq = fmaf(x, x, qq);
-                kk = fmaf(y, y, kk);
+            for (int offset = group >> 1; offset > 0; offset >>= 1) {
+                qq += __shfl_xor_sync(0xffffffffu, qq, offset);
+                kk += __shfl_xor_sync(0xffffffffu, kk, offset);
             }
-            qq = pl_warp_sum(qq);
-            kk = pl_warp_sum(kk);
-            if (lane == 0) {
+            if (c < n && sub == 0) {
                 inv_q[c] = p.q_scale / sqrtf(qq + p.unit_eps);
                 inv_k[c] = 1.0f / sqrtf(kk + p.unit_eps);
                 sb[c] = 1.0f / (1.0f + expf(-b));
@@ -468,17 +725,29 @@ PL_API int pl_gated_delta(const void* q, const void* k, const void* v, int64_t q
     }
     int threads = ((cols * parts + 31) / 32) * 32;
     const size_t elem = dtype == PL_F32 ? 4 : 2;
+    // Key sizes 16, 32, 64 and 128 with a full block of columns: the form with the sizes known to the
+    // compiler and half of its CTA making chunks ready (256 threads, two buffers of vectors).
+    const bool fixed = (dim == 16 || dim == 32 || dim == 64 || dim == 128) && cols * parts == 128;
     auto bytes_for = [&](int chunk) {
-        const size_t vectors = ((static_cast<size_t>(chunk) * (3 * dim + 3) + 3) / 4 * 4 + (dim + 3) / 4 * 4) * sizeof(float);
         const size_t raw = (static_cast<size_t>(chunk) * (3 * dim + cols) * elem + 15) / 16 * 16;
+        if (fixed) {
+            const size_t vec = (static_cast<size_t>(chunk) * (3 * dim + cols + 1) + 3) / 4 * 4;
+            return (2 * vec + (2 * static_cast<size_t>(chunk) + 3) / 4 * 4 + dim) * sizeof(float) + 2 * raw;
+        }
+        const size_t vectors = ((static_cast<size_t>(chunk) * (3 * dim + 3) + 3) / 4 * 4 + (dim + 3) / 4 * 4) * sizeof(float);
         return vectors + 2 * raw;
     };
     int chunk = kChunkMost;
-    while (chunk > 1 && bytes_for(chunk) > 44 * 1024) {
+    while (chunk > 1 && bytes_for(chunk) > (fixed ? 96 : 44) * 1024) {
         chunk /= 2;
     }
     const size_t smem = bytes_for(chunk);
     PL_REQUIRE(smem <= 200 * 1024, "gated_delta: key size %d needs too much shared memory", dim);
+    // A step that brings at most two tokens an entry has nothing to make ready ahead: the form without
+    // the second half (the same chunk size, so the same sums).
+    const bool few = fixed && n_tokens <= 2 * n_entries;
+    const size_t smem_single = ((static_cast<size_t>(chunk) * (3 * dim + 3) + 3) / 4 * 4 + (dim + 3) / 4 * 4) * sizeof(float) +
+        2 * ((static_cast<size_t>(chunk) * (3 * dim + cols) * elem + 15) / 16 * 16);
     const int per = static_cast<int>(16 / elem);
     const int async_loads = dim % per == 0 && cols % per == 0 && vdim % per == 0 && qkv_stride % per == 0 &&
         a_stride % per == 0 &&
@@ -491,28 +760,44 @@ PL_API int pl_gated_delta(const void* q, const void* k, const void* v, int64_t q
     p.vdim = vdim; p.parts = parts; p.cols = cols; p.chunk = chunk; p.async_loads = async_loads; p.unit_eps = unit_eps; p.q_scale = q_scale;
     const dim3 grid(n_entries, n_heads, (vdim + cols - 1) / cols);
     const int n_pairs = n_tokens * n_heads;
+#define PL_SCAN_STATIC(D, P)                                                                                        \
+    do {                                                                                                               \
+        if (smem > 48 * 1024) {                                                                                        \
+            cudaFuncSetAttribute(gated_delta_scan_static_kernel<scalar_t, D, P>,                                       \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));                 \
+        }                                                                                                              \
+        if (few) {                                                                                                     \
+            if (smem_single > 48 * 1024) {                                                                             \
+                cudaFuncSetAttribute(gated_delta_scan_static_single_kernel<scalar_t, D, P>,                            \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_single));      \
+            }                                                                                                          \
+            pl_launch_overlapped(gated_delta_scan_static_single_kernel<scalar_t, D, P>, grid, dim3(128), smem_single,   \
+                                 stream, p);                                                                           \
+        } else {                                                                                                       \
+            pl_launch_overlapped(gated_delta_scan_static_kernel<scalar_t, D, P>, grid, dim3(256), smem, stream, p);    \
+        }                                                                                                              \
+    } while (0)
     PL_DISPATCH_DTYPE(dtype, "gated_delta", {
-        if (smem > 48 * 1024) {
-            cudaFuncSetAttribute(gated_delta_scan_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem));
-        }
-        // Key sizes 16, 32, 64 and 128 with 128 threads: the form with the sizes known to the compiler.
-        const bool fixed = threads == 128 && (dim == 16 || dim == 32 || dim == 64 || dim == 128) && smem <= 48 * 1024;
         if (fixed && dim == 16) {
-            pl_launch_overlapped(gated_delta_scan_static_kernel<scalar_t, 16, 1>, grid, dim3(threads), smem, stream, p);
+            PL_SCAN_STATIC(16, 1);
         } else if (fixed && dim == 32) {
-            pl_launch_overlapped(gated_delta_scan_static_kernel<scalar_t, 32, 2>, grid, dim3(threads), smem, stream, p);
+            PL_SCAN_STATIC(32, 2);
         } else if (fixed && dim == 64) {
-            pl_launch_overlapped(gated_delta_scan_static_kernel<scalar_t, 64, 4>, grid, dim3(threads), smem, stream, p);
+            PL_SCAN_STATIC(64, 4);
         } else if (fixed && dim == 128) {
-            pl_launch_overlapped(gated_delta_scan_static_kernel<scalar_t, 128, 8>, grid, dim3(threads), smem, stream, p);
+            PL_SCAN_STATIC(128, 8);
         } else {
+            if (smem > 48 * 1024) {
+                cudaFuncSetAttribute(gated_delta_scan_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem));
+            }
             pl_launch_overlapped(gated_delta_scan_kernel<scalar_t>, grid, dim3(threads), smem, stream, p);
         }
         pl_launch_overlapped(gated_delta_finish_kernel<scalar_t>, dim3((n_pairs + 3) / 4), dim3(128), 0, stream,
                              static_cast<const float*>(o_raw), norm, static_cast<const scalar_t*>(gate_pre), gate_stride,
                              static_cast<scalar_t*>(out), out_stride, n_pairs, n_heads, vdim, eps);
     });
+#undef PL_SCAN_STATIC
     PL_CHECK_LAUNCH("gated_delta");
     return 0;
 }
