@@ -40,11 +40,35 @@ __device__ __forceinline__ void warp_argmax(float& value, int& index) {
     }
 }
 
+template <typename scalar_t>
+struct Vec;
+template <>
+struct Vec<float> {
+    static constexpr int kCount = 4;
+    __device__ static __forceinline__ void load(const float* p, float* out) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    }
+};
+template <>
+struct Vec<__nv_bfloat16> {
+    static constexpr int kCount = 8;
+    __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* out) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            out[2 * i] = __uint_as_float(words[i] << 16);
+            out[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+        }
+    }
+};
+
 // TOKENS tokens per block (a long step reads the router's weights once per TOKENS tokens): the
 // logits by a warp per expert for all of the block's tokens at once, then a warp per token
 // chooses. A token's sums are the same whatever TOKENS is.
 template <typename scalar_t, int TOKENS>
-__global__ void moe_route_kernel(const scalar_t* __restrict__ h, int64_t h_stride, const float* __restrict__ router,
+__global__ void __launch_bounds__(512, TOKENS > 1 ? 2 : 1) moe_route_kernel(const scalar_t* __restrict__ h, int64_t h_stride, const float* __restrict__ router,
                                  const float* __restrict__ correction, int32_t* __restrict__ ids,
                                  float* __restrict__ weights, int n_tokens, int hidden, int n_experts, int top,
                                  int n_groups, int keep) {
@@ -58,9 +82,32 @@ __global__ void moe_route_kernel(const scalar_t* __restrict__ h, int64_t h_strid
     const int t0 = blockIdx.x * TOKENS;
     const int here = min(TOKENS, n_tokens - t0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    for (int i = threadIdx.x; i < TOKENS * hidden; i += blockDim.x) {
-        const int r = i / hidden;
-        rows[i] = r < here ? pl_load(h + static_cast<int64_t>(t0 + r) * h_stride + (i - r * hidden)) : 0.0f;
+    constexpr int kPer = Vec<scalar_t>::kCount;  // elements of a 16-byte load
+    if (hidden % kPer == 0 && h_stride % kPer == 0 && (reinterpret_cast<uintptr_t>(h) & 15) == 0) {
+        // 16 bytes of a row per thread and turn, several turns' loads in flight
+        const int per_row = hidden / kPer;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < TOKENS * per_row; i += blockDim.x) {
+            const int r = i / per_row, j = (i - r * per_row) * kPer;
+            float x[kPer];
+            if (r < here) {
+                Vec<scalar_t>::load(h + static_cast<int64_t>(t0 + r) * h_stride + j, x);
+            } else {
+#pragma unroll
+                for (int u = 0; u < kPer; ++u) {
+                    x[u] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kPer; u += 4) {
+                *reinterpret_cast<float4*>(rows + r * hidden + j + u) = make_float4(x[u], x[u + 1], x[u + 2], x[u + 3]);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < TOKENS * hidden; i += blockDim.x) {
+            const int r = i / hidden;
+            rows[i] = r < here ? pl_load(h + static_cast<int64_t>(t0 + r) * h_stride + (i - r * hidden)) : 0.0f;
+        }
     }
     __syncthreads();
     const bool vectors = (hidden & 3) == 0 && (reinterpret_cast<uintptr_t>(router) & 15) == 0;
@@ -74,7 +121,7 @@ __global__ void moe_route_kernel(const scalar_t* __restrict__ h, int64_t h_strid
         if (vectors) {
             // Eight of the lane's vectors of the expert's row are asked for before any is used (the row
             // comes from L2 or memory: one load at a time would make a chain of their latencies).
-            constexpr int kAhead = 8;
+            constexpr int kAhead = TOKENS > 1 ? 4 : 8;
             for (int base = lane * 4; base < hidden; base += 128 * kAhead) {
                 float4 wv[kAhead];
 #pragma unroll
@@ -202,30 +249,6 @@ __global__ void moe_route_kernel(const scalar_t* __restrict__ h, int64_t h_strid
         weights[static_cast<int64_t>(t) * top + j] *= inv;
     }
 }
-
-template <typename scalar_t>
-struct Vec;
-template <>
-struct Vec<float> {
-    static constexpr int kCount = 4;
-    __device__ static __forceinline__ void load(const float* p, float* out) {
-        const float4 v = *reinterpret_cast<const float4*>(p);
-        out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
-    }
-};
-template <>
-struct Vec<__nv_bfloat16> {
-    static constexpr int kCount = 8;
-    __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* out) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(p);
-        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            out[2 * i] = __uint_as_float(words[i] << 16);
-            out[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
-        }
-    }
-};
 
 // Dot product of a weight row with an fp32 vector in shared memory over a warp: lane l takes
 // the elements of vectors l, l + 32, ...; the lanes' sums are added as a tree.
@@ -612,6 +635,8 @@ PL_API int pl_moe_route(const void* h, int64_t h_stride, const float* router, co
                 cudaFuncSetAttribute(moe_route_kernel<scalar_t, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem));
             }
+            // (room for two of these CTAs' rows per SM)
+            cudaFuncSetAttribute(moe_route_kernel<scalar_t, 8>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
             pl_launch_overlapped(moe_route_kernel<scalar_t, 8>, dim3((n_tokens + 7) / 8), dim3(threads), smem, stream,
                                  static_cast<const scalar_t*>(h), h_stride, router, correction, ids, weights, n_tokens,
                                  hidden, n_experts, top, n_groups, keep);

@@ -529,6 +529,21 @@ def test_head_counts_and_row_sizes_with_and_without_a_tensor_core_kernel(heads, 
         tm.check(tokens, harness.replay(tm.runner(16), steps), f"heads {heads}/{kv_heads} of {dim}, {vdim}")
 
 
+@pytest.mark.parametrize("width", [50, 70])
+def test_widths_that_are_no_multiple_of_four(width):
+    """No 16-byte rows anywhere: every kernel's element-by-element form, in both dtypes."""
+    cfg = {"architecture": "Bunosun", "vocab": 67, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.5},
+           "layers": [bt.attention_layer(2, 1, 10, 14, 11, 6, bt.moe(6, 2, 22, 3, 2, 18), diff=0.3, factor=2.0),
+                      bt.delta_layer(2, 1, 10, 14, 3, bt.moe(6, 2, 22, 3, 2, 18))],
+           "loop": {"start": 0, "stop": 2, "times": 2}}
+    for dtype in ("float32", "bfloat16"):
+        tm = bt.TinyBunosun("-", dtype, cfg=cfg, seed=2)
+        tokens = {"p": bt.random_tokens(cfg, 90, 70)}
+        steps = [([("p", tokens["p"][:60], list(range(60)))], [])]
+        steps += [([("p", [t], [0])], []) for t in tokens["p"][60:]]
+        tm.check(tokens, harness.replay(tm.runner(8), steps), f"width {width}")
+
+
 def test_missing_and_misshapen_tensors_are_named():
     from pulsarlm_b200.engine.loading import load_model
     from pulsarlm_b200.weights.loader import WeightsError
