@@ -381,10 +381,9 @@ __global__ void moe_gate_up_kernel(const scalar_t* __restrict__ h, int64_t h_str
     if (f0 + kFeaturesPerWarp <= ff) {
         // The warp's four gate rows are neighbours, and so are its up rows: eight loads in flight per lane.
         float g[kFeaturesPerWarp], u[kFeaturesPerWarp];
-        warp_dots<scalar_t, kFeaturesPerWarp>(weights + static_cast<int64_t>(f0) * hidden, hidden, row, hidden, vectors,
-                                              lane, g);
-        warp_dots<scalar_t, kFeaturesPerWarp>(weights + static_cast<int64_t>(ff + f0) * hidden, hidden, row, hidden,
-                                              vectors, lane, u);
+        warp_dots_two<scalar_t, kFeaturesPerWarp>(weights + static_cast<int64_t>(f0) * hidden, row,
+                                                  weights + static_cast<int64_t>(ff + f0) * hidden, row, hidden, hidden,
+                                                  vectors, lane, g, u);
         if (lane < kFeaturesPerWarp) {
             float gl = g[0], ul = u[0];
 #pragma unroll
