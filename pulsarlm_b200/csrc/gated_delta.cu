@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(const GatedDeltaP
 
 // The same scan with the key size and the lanes per column known to the compiler, and with the
 // work split between two halves of the CTA: warps 0 to 3 hold the state's columns (a lane holds
-// DIM / PARTS = 16 consecutive rows of its column, reads its share of q^, k^ and g with 16-byte
+// DIM / PARTS = 8 consecutive rows of its column, reads its share of q^, k^ and g with 16-byte
 // loads one token ahead of the token whose chain it is in) and do nothing but the tokens'
 // updates, one chunk after the other; warps 4 to 7 meanwhile make the next chunk ready: they
 // ask for the chunk after it (cp.async), turn the one that has arrived into the fp32 vectors
@@ -299,12 +299,12 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(const GatedDeltaP
 // alone. (A lane's rows differ from the kernel above, so the sums' order does; which kernel
 // runs depends on the sizes alone.)
 template <typename scalar_t, int DIM, int PARTS>
-__global__ void __launch_bounds__(256) gated_delta_scan_static_kernel(const GatedDeltaParams p) {
+__global__ void __launch_bounds__(256, 1) gated_delta_scan_static_kernel(const GatedDeltaParams p) {
     pl_grid_trigger();
     pl_grid_wait();
     constexpr int R = DIM / PARTS;      // rows per lane
     constexpr int COLS = 128 / PARTS;   // value columns per CTA
-    static_assert(R == kRows, "a lane holds sixteen rows");
+    static_assert(R % 4 == 0 && R <= kRows, "a lane holds a multiple of four rows");
     extern __shared__ __align__(16) unsigned char smem[];
     const int chunk = p.chunk;
     // two buffers of a chunk's vectors: [chunk][DIM] q^, k^, g, [chunk][COLS] v, [chunk] b (rounded up to 4 floats)
@@ -505,7 +505,7 @@ __global__ void __launch_bounds__(128) gated_delta_scan_static_single_kernel(con
     pl_grid_trigger();
     pl_grid_wait();
     constexpr int R = DIM / PARTS;  // rows per lane
-    static_assert(R == kRows, "a lane holds sixteen rows");
+    static_assert(R % 4 == 0 && R <= kRows, "a lane holds a multiple of four rows");
     extern __shared__ __align__(16) unsigned char smem[];
     const int chunk = p.chunk, cols = p.cols;
     float* sq = reinterpret_cast<float*>(smem);
@@ -727,7 +727,13 @@ PL_API int pl_gated_delta(const void* q, const void* k, const void* v, int64_t q
     const size_t elem = dtype == PL_F32 ? 4 : 2;
     // Key sizes 16, 32, 64 and 128 with a full block of columns: the form with the sizes known to the
     // compiler and half of its CTA making chunks ready (256 threads, two buffers of vectors).
-    const bool fixed = (dim == 16 || dim == 32 || dim == 64 || dim == 128) && cols * parts == 128;
+    // (there a lane holds eight rows: shorter chains of additions per token, more CTAs per head)
+    const bool fixed = (dim == 16 || dim == 32 || dim == 64 || dim == 128) && vdim >= 128 / (dim / 8);
+    if (fixed) {
+        parts = dim / 8;
+        cols = 128 / parts;
+        threads = 128;
+    }
     auto bytes_for = [&](int chunk) {
         const size_t raw = (static_cast<size_t>(chunk) * (3 * dim + cols) * elem + 15) / 16 * 16;
         if (fixed) {
@@ -779,13 +785,13 @@ PL_API int pl_gated_delta(const void* q, const void* k, const void* v, int64_t q
     } while (0)
     PL_DISPATCH_DTYPE(dtype, "gated_delta", {
         if (fixed && dim == 16) {
-            PL_SCAN_STATIC(16, 1);
+            PL_SCAN_STATIC(16, 2);
         } else if (fixed && dim == 32) {
-            PL_SCAN_STATIC(32, 2);
+            PL_SCAN_STATIC(32, 4);
         } else if (fixed && dim == 64) {
-            PL_SCAN_STATIC(64, 4);
+            PL_SCAN_STATIC(64, 8);
         } else if (fixed && dim == 128) {
-            PL_SCAN_STATIC(128, 8);
+            PL_SCAN_STATIC(128, 16);
         } else {
             if (smem > 48 * 1024) {
                 cudaFuncSetAttribute(gated_delta_scan_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
